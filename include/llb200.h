@@ -22,7 +22,7 @@
 extern "C" {
 #endif
 
-#define LL_ABI_VERSION 13
+#define LL_ABI_VERSION 14
 
 #define LL_OK 0
 #define LL_ERR_ARG (-1)         /* bad shape / dtype / null pointer */
@@ -450,13 +450,18 @@ LL_API int ll_moe_combine(const void* y, const float* expert_w, int top, const v
 LL_API int ll_add_norm_pair(float* x, const void* a0, float s0, const void* a1, float s1, const void* a2, float s2, const float* w1,
                             const float* w2, float eps, void* out1, int out1_f32, void* out2, int act_dtype, int rows, int dim,
                             ll_stream stream);
-/* RMS norm of fp32 rows y [rows][C] in `groups` equal parts with a silu gate (activation dtype, row stride gate_stride):
- * gate_first 1: (y * silu(g)) / rms_part(.) * w;  0: y / rms_part(y) * w * silu(g).  w: C entries, or C / groups shared by the
- * parts (w_shared). */
-LL_API int ll_gated_group_norm(const float* y, const void* gate, int gate_stride, const float* w, int w_shared, float eps, int groups,
-                               int gate_first, void* out, int act_dtype, int rows, int C, ll_stream stream);
+/* RMS norm of fp32 rows y in `groups` equal parts with a gate (activation dtype, row stride gate_stride; silu, or a sigmoid
+ * when gate_sigmoid):  gate_first 1: (y * gate(g)) / rms_part(.) * w;  0: y / rms_part(y) * w * gate(g).  w: C entries, or
+ * C / groups shared by the parts (w_shared).  A part of y spans y_gs numbers (0: C / groups), of which the first C / groups are
+ * normed.  stab (fp32 [rows][groups], optional): number C / groups of every part is a normaliser's product nq and stab the
+ * stabiliser mx; the part is divided by max(|nq|, exp(-mx)) + 1e-6 before the norm. */
+LL_API int ll_gated_group_norm(const float* y, int y_gs, const float* stab, const void* gate, int gate_stride, const float* w,
+                               int w_shared, float eps, int groups, int gate_first, int gate_sigmoid, void* out, int act_dtype,
+                               int rows, int C, ll_stream stream);
 /* h <- relu(h)^2, in place */
 LL_API int ll_relu_squared(void* h, int dtype, size_t n, ll_stream stream);
+/* h <- gelu(h), in place: 0.5 h (1 + erf(h / sqrt 2)), or with tanh_form 0.5 h (1 + tanh(sqrt(2/pi) (h + 0.044715 h^3))) */
+LL_API int ll_gelu(void* h, int dtype, int tanh_form, size_t n, ll_stream stream);
 
 /* ---------------------------------------------------------------------------------------
  * Short causal convolution with state (csrc/short_conv.cu)
@@ -476,10 +481,18 @@ LL_API int ll_short_conv(const void* x, int x_dtype, int x_stride, int col0, con
 /* Per (b, h): S_t[i][c] = a_t[i] S_(t-1)[i][c] + ks_t k_t[i] v_t[c];  y_t[c] = qs sum_i q_t[i] S_t[i][c] + skip[h] v_t[c].
  * q, k: [B*T][stride], head g = h / (H / qk_heads) at columns g*n..; v: head h at columns h*p..; a: fp32 [B*T][H][n]
  * (a_per_channel) or [B*T][H]; ks fp32 [B*T][H] or NULL; skip fp32 [H] or NULL; state fp32 [B][H][n][p] (read unless
- * pos_ids[0] == 0, replaced); y fp32 [B*T][H*p]. */
+ * pos_ids[0] == 0, replaced); y fp32 [B*T][H*p].  unit_col: the last of the p columns of every head is the constant 1 and v
+ * holds p - 1 columns per head (that column of S sums the keys alone: a normaliser carried by the same walk). */
 LL_API int ll_decay_scan(const void* q, int q_stride, const void* k, int k_stride, const void* v, int v_stride, int dtype,
                          const float* a, int a_per_channel, const float* ks, const float* skip, float qs, float* state,
-                         const int32_t* pos_ids, float* y, int B, int T, int H, int qk_heads, int n, int p, ll_stream stream);
+                         const int32_t* pos_ids, float* y, int B, int T, int H, int qk_heads, int n, int p, int unit_col,
+                         ll_stream stream);
+/* Exponential gates with a running stabiliser, per (b, h): li = cap(raw_i + bias_i[h]), lf = logsigmoid(cap(raw_f + bias_f[h])),
+ * cap(z) = c tanh(z / c) (c <= 0: none); mx_t = max(lf_t + mx_(t-1), li_t) with mx carried in mstate fp32 [B][H] (0 when
+ * pos_ids[0] == 0); keep = exp(lf + mx_(t-1) - mx_t), take = exp(li - mx_t), stab = mx_t   (fp32 [B*T][H] each). */
+LL_API int ll_matrix_memory_gates(const void* raw_i, const void* raw_f, int dtype, int stride, const float* bias_i,
+                                  const float* bias_f, float cap, float* mstate, const int32_t* pos_ids, float* keep, float* take,
+                                  float* stab, int B, int T, int H, ll_stream stream);
 /* dt = softplus(raw[m][h] + dt_bias[h]); decay = exp(-exp(a_log[h]) dt)   (fp32 [M][H] each) */
 LL_API int ll_ssm_gates(const void* raw, int dtype, int stride, const float* dt_bias, const float* a_log, float* dt_out,
                         float* decay, int M, int H, ll_stream stream);
@@ -502,6 +515,28 @@ LL_API int ll_window_attn(const void* q, int q_stride, const void* gate, int gat
                           const int32_t* pos_ids, const float* r1, const float* r2, const float* talk, float scale, float softcap,
                           int B, int T, int H, int G, int dim, int vdim, int window, int keep, int ring, int splits, float* scratch,
                           void* y, ll_stream stream);
+
+/* ---------------------------------------------------------------------------------------
+ * Softmax attention with rotary positions over a ring of rows (csrc/rotary_attn.cu)
+ * ------------------------------------------------------------------------------------- */
+
+/* Rows of this step: q (H heads of dim) and k (G heads of dim; NULL: queries only) get an optional RMS norm over the whole
+ * row times q_norm / k_norm (fp32, NULL: none), then the first rot_dims dimensions of every head turn by position * freq[i]
+ * (fp32 [rot_dims / 2]; dimension i pairs with i + rot_dims / 2).  q -> q_out [B*T][H*dim]; k -> kc [B][ring][G*dim] at slot
+ * position % ring; vc [B][ring][G*vdim] gets v, or (v NULL, vdim == dim) the keys as they are before the rotation. */
+LL_API int ll_qk_rotary_append(const void* q, int q_stride, const void* k, int k_stride, const void* v, int v_stride, int dtype,
+                               const float* q_norm, const float* k_norm, float eps, const float* freq, int rot_dims,
+                               const int32_t* pos_ids, void* q_out, void* kc, void* vc, int B, int T, int H, int G, int dim, int vdim,
+                               int ring, ll_stream stream);
+/* s_h(i,j) = scale q_h(i).k_g(j), then cap tanh(s / cap) (softcap 0: none); j visible when j <= i, (window 0 or i - j < window),
+ * (chunk 0 or j / chunk == i / chunk); softmax with exp(sink[h]) added to the denominator (sink NULL: none); o_h = sum_j w v_g(j),
+ * times sigmoid(gate[m][h*vdim + c]) (gate NULL: none) -> y [B*T][H*vdim].  form 0: chosen by shape and dtype; 1: the fp32
+ * form.  splits > 1 cuts every query's keys into that many ranges (fp32 form; scratch: ll_softmax_attn_scratch_bytes). */
+LL_API size_t ll_softmax_attn_scratch_bytes(int M, int H, int vdim, int splits);
+LL_API int ll_softmax_attn(const void* q, int q_stride, const void* gate, int gate_stride, const void* kc, const void* vc, int dtype,
+                           const int32_t* pos_ids, const float* sink, float scale, float softcap, int B, int T, int H, int G, int dim,
+                           int vdim, int window, int chunk, int ring, int splits, int form, float* scratch, void* y,
+                           ll_stream stream);
 
 #ifdef __cplusplus
 }

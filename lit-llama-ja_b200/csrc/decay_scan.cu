@@ -8,6 +8,10 @@
 // projection outputs in the activation dtype; a (the decay itself, in (0, 1]), ks and skip are fp32; S and y are fp32 and
 // every product and sum is fp32.  The state is carried in `state[B][H][n][p]`; a sequence at position 0 starts from zero
 // whatever the state holds.
+//
+// unit_col: the LAST of the p columns of every head is not in memory but the constant 1 (v then holds p - 1 columns per
+// head).  That column of S is the running sum of the keys alone and that column of y its product with the query: the
+// normaliser of a matrix memory, carried by the same walk.
 #include "common.cuh"
 
 namespace llb {
@@ -26,7 +30,7 @@ __global__ void __launch_bounds__(DS_THREADS) decay_scan_kernel(
     const T* __restrict__ q, int q_stride, const T* __restrict__ k, int k_stride, const T* __restrict__ v, int v_stride,
     const float* __restrict__ a, int a_per_channel, const float* __restrict__ ks, const float* __restrict__ skip, float qs,
     float* __restrict__ state, const int32_t* __restrict__ pos_ids, float* __restrict__ y, int Tn, int H, int qk_heads, int n,
-    int p) {
+    int p, int vw) {
   constexpr int PT = DS_THREADS / NP;
   constexpr int NPAD = NP * DS_NL;
   constexpr int DS_TC = ds_tc(NPAD);
@@ -66,8 +70,8 @@ __global__ void __launch_bounds__(DS_THREADS) decay_scan_kernel(
       const int idx = it * DS_THREADS + threadIdx.x;
       const int tt = idx / PT, cc = idx - tt * PT;
       const int col = blockIdx.x * PT + cc;
-      const bool ok = tt < DS_TC && t0 + tt < Tn && col < p;
-      rv[it] = v[ok ? ((size_t)b * Tn + t0 + tt) * v_stride + (size_t)h * p + col : 0];
+      const bool ok = tt < DS_TC && t0 + tt < Tn && col < vw;
+      rv[it] = v[ok ? ((size_t)b * Tn + t0 + tt) * v_stride + (size_t)h * vw + col : 0];
     }
   };
   fetch(0);
@@ -87,7 +91,10 @@ __global__ void __launch_bounds__(DS_THREADS) decay_scan_kernel(
     for (int it = 0; it < VIT; ++it) {
       const int idx = it * DS_THREADS + threadIdx.x;
       const int tt = idx / PT, cc = idx - tt * PT;
-      if (tt < DS_TC) s_v[tt][cc] = (t0 + tt < Tn && blockIdx.x * PT + cc < p) ? dt<T>::ld(&rv[it], 0) : 0.f;
+      if (tt < DS_TC) {
+        const int col = blockIdx.x * PT + cc;
+        s_v[tt][cc] = (t0 + tt < Tn && col < p) ? (col < vw ? dt<T>::ld(&rv[it], 0) : 1.f) : 0.f;
+      }
     }
     __syncthreads();
     if (t0 + DS_TC < Tn) fetch(t0 + DS_TC);
@@ -128,15 +135,15 @@ __global__ void __launch_bounds__(DS_THREADS) decay_scan_kernel(
 template <typename T, int NP, int NL>
 static int decay_scan_launch(const void* q, int q_stride, const void* k, int k_stride, const void* v, int v_stride, const float* a,
                              int a_per_channel, const float* ks, const float* skip, float qs, float* state, const int32_t* pos_ids,
-                             float* y, int B, int Tn, int H, int qk_heads, int n, int p, cudaStream_t st) {
+                             float* y, int B, int Tn, int H, int qk_heads, int n, int p, int vw, cudaStream_t st) {
   constexpr int PT = DS_THREADS / NP;
   const dim3 grid((p + PT - 1) / PT, H, B);
   if (a_per_channel)
     decay_scan_kernel<T, NP, NL, true><<<grid, DS_THREADS, 0, st>>>((const T*)q, q_stride, (const T*)k, k_stride, (const T*)v, v_stride, a, 1,
-                                                                    ks, skip, qs, state, pos_ids, y, Tn, H, qk_heads, n, p);
+                                                                    ks, skip, qs, state, pos_ids, y, Tn, H, qk_heads, n, p, vw);
   else
     decay_scan_kernel<T, NP, NL, false><<<grid, DS_THREADS, 0, st>>>((const T*)q, q_stride, (const T*)k, k_stride, (const T*)v, v_stride, a, 0,
-                                                                     ks, skip, qs, state, pos_ids, y, Tn, H, qk_heads, n, p);
+                                                                     ks, skip, qs, state, pos_ids, y, Tn, H, qk_heads, n, p, vw);
   LL_LAUNCH_OK("decay_scan_kernel");
   return LL_OK;
 }
@@ -170,6 +177,52 @@ __global__ void channel_decay_kernel(const T* __restrict__ z, int stride, const 
   out[i] = expf(-sp * inv_tau);
 }
 
+// Exponential gates of a matrix memory with a running stabiliser.  Per (sequence, head), with raw_i / raw_f column slices
+// of the input projection's output, li = cap(raw_i + bi), lf = logsigmoid(cap(raw_f + bf)), cap(z) = c tanh(z / c) (c <= 0:
+// no cap), and mx carried from token to token (0 at a sequence's start, not minus infinity):
+//   mx_t = max(lf_t + mx_(t-1), li_t);   keep_t = exp(lf_t + mx_(t-1) - mx_t);   take_t = exp(li_t - mx_t)
+// A warp owns one (sequence, head): 32 tokens are loaded and turned into (li, lf) in parallel, the walk over them runs in
+// registers of every lane alike (two shuffles a token), lane t keeps token t's results.
+template <typename T>
+__global__ void matrix_memory_gates_kernel(const T* __restrict__ raw_i, const T* __restrict__ raw_f, int stride,
+                                           const float* __restrict__ bias_i, const float* __restrict__ bias_f, float cap,
+                                           float* __restrict__ mstate, const int32_t* __restrict__ pos_ids, float* __restrict__ keep,
+                                           float* __restrict__ take, float* __restrict__ stab, int Tn, int H, int BH) {
+  const int w = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (w >= BH) return;
+  const int lane = threadIdx.x & 31;
+  const int b = w / H, h = w - b * H;
+  float mx = pos_ids[0] == 0 ? 0.f : mstate[w];
+  const float bi = bias_i ? bias_i[h] : 0.f, bf = bias_f ? bias_f[h] : 0.f;
+  const float inv = cap > 0.f ? 1.f / cap : 0.f;
+  for (int t0 = 0; t0 < Tn; t0 += 32) {
+    const int t = t0 + lane;
+    float li = 0.f, lf = 0.f;
+    if (t < Tn) {
+      const size_t m = (size_t)b * Tn + t;
+      float zi = dt<T>::ld(raw_i, m * stride + h) + bi, zf = dt<T>::ld(raw_f, m * stride + h) + bf;
+      if (cap > 0.f) zi = cap * tanhf(zi * inv), zf = cap * tanhf(zf * inv);
+      li = zi;
+      lf = fminf(zf, 0.f) - log1pf(expf(-fabsf(zf)));          // log sigmoid
+    }
+    const int nt = min(32, Tn - t0);
+    float my_prev = 0.f, my_new = 0.f;
+    for (int tt = 0; tt < nt; ++tt) {
+      const float f = __shfl_sync(0xffffffffu, lf, tt), i = __shfl_sync(0xffffffffu, li, tt);
+      const float mn = fmaxf(f + mx, i);
+      if (lane == tt) my_prev = mx, my_new = mn;
+      mx = mn;
+    }
+    if (t < Tn) {
+      const size_t o = ((size_t)b * Tn + t) * H + h;
+      keep[o] = expf(lf + my_prev - my_new);
+      take[o] = expf(li - my_new);
+      stab[o] = my_new;
+    }
+  }
+  if (lane == 0) mstate[w] = mx;
+}
+
 }  // namespace llb
 
 using namespace llb;
@@ -178,9 +231,11 @@ extern "C" {
 
 int ll_decay_scan(const void* q, int q_stride, const void* k, int k_stride, const void* v, int v_stride, int dtype, const float* a,
                   int a_per_channel, const float* ks, const float* skip, float qs, float* state, const int32_t* pos_ids, float* y,
-                  int B, int T, int H, int qk_heads, int n, int p, ll_stream stream) {
+                  int B, int T, int H, int qk_heads, int n, int p, int unit_col, ll_stream stream) {
   LL_CHECK_ARG(q && k && v && a && state && pos_ids && y, "decay_scan: null pointer");
-  LL_CHECK_ARG(B >= 0 && T >= 0 && H > 0 && qk_heads > 0 && H % qk_heads == 0 && n > 0 && p > 0, "bad decay_scan arguments");
+  LL_CHECK_ARG(B >= 0 && T >= 0 && H > 0 && qk_heads > 0 && H % qk_heads == 0 && n > 0 && p > (unit_col ? 1 : 0),
+               "bad decay_scan arguments");
+  const int vw = unit_col ? p - 1 : p;
   if (n > 32 * 16) {
     set_error("decay_scan: %d state rows per head (up to %d)", n, 32 * 16);
     return LL_ERR_UNSUPPORTED;
@@ -197,9 +252,9 @@ int ll_decay_scan(const void* q, int q_stride, const void* k, int k_stride, cons
   while (np * nl < n) np *= 2;
 #define LL_DS(TT, NP)                                                                                                                 \
   return nl == 8 ? decay_scan_launch<TT, NP, 8>(q, q_stride, k, k_stride, v, v_stride, a, a_per_channel, ks, skip, qs, state, pos_ids, \
-                                                y, B, T, H, qk_heads, n, p, st)                                                        \
+                                                y, B, T, H, qk_heads, n, p, vw, st)                                                        \
                  : decay_scan_launch<TT, NP, 16>(q, q_stride, k, k_stride, v, v_stride, a, a_per_channel, ks, skip, qs, state, pos_ids, \
-                                                 y, B, T, H, qk_heads, n, p, st)
+                                                 y, B, T, H, qk_heads, n, p, vw, st)
 #define LL_DS_T(TT)                 \
   switch (np) {                     \
     case 1: LL_DS(TT, 1);           \
@@ -250,6 +305,29 @@ int ll_channel_decay(const void* z, int dtype, int stride, const float* bias, fl
     return LL_ERR_UNSUPPORTED;
   }
   LL_LAUNCH_OK("channel_decay_kernel");
+  return LL_OK;
+}
+
+int ll_matrix_memory_gates(const void* raw_i, const void* raw_f, int dtype, int stride, const float* bias_i, const float* bias_f,
+                           float cap, float* mstate, const int32_t* pos_ids, float* keep, float* take, float* stab, int B, int T, int H,
+                           ll_stream stream) {
+  LL_CHECK_ARG(raw_i && raw_f && mstate && pos_ids && keep && take && stab && B >= 0 && T >= 0 && H > 0 && stride >= H,
+               "bad matrix_memory_gates arguments");
+  if (B == 0 || T == 0) return LL_OK;
+  cudaStream_t st = (cudaStream_t)stream;
+  const int BH = B * H;
+  const unsigned blocks = (unsigned)((BH + 3) / 4);
+  if (dtype == LL_F32)
+    matrix_memory_gates_kernel<float><<<blocks, 128, 0, st>>>((const float*)raw_i, (const float*)raw_f, stride, bias_i, bias_f, cap, mstate,
+                                                             pos_ids, keep, take, stab, T, H, BH);
+  else if (dtype == LL_BF16)
+    matrix_memory_gates_kernel<__nv_bfloat16><<<blocks, 128, 0, st>>>((const __nv_bfloat16*)raw_i, (const __nv_bfloat16*)raw_f, stride,
+                                                                     bias_i, bias_f, cap, mstate, pos_ids, keep, take, stab, T, H, BH);
+  else {
+    set_error("matrix_memory_gates: unsupported dtype %d", dtype);
+    return LL_ERR_UNSUPPORTED;
+  }
+  LL_LAUNCH_OK("matrix_memory_gates_kernel");
   return LL_OK;
 }
 

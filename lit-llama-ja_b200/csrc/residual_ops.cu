@@ -196,26 +196,31 @@ __global__ void add_norm_pair_kernel(float* __restrict__ x, const TA* __restrict
   }
 }
 
-// RMS norm of an fp32 row in `groups` equal parts (each by its own root mean square), a weight, and a silu gate:
-//   gate_first: t = y * silu(g);  out = t / rms_part(t) * w          (the gate enters the norm)
-//   otherwise : out = y / rms_part(y) * w * silu(g)                  (the gate follows the norm)
+// RMS norm of an fp32 row in `groups` equal parts (each by its own root mean square), a weight, and a gate (silu, or a
+// sigmoid when gate_sigmoid):
+//   gate_first: t = y * gate(g);  out = t / rms_part(t) * w          (the gate enters the norm)
+//   otherwise : out = y / rms_part(y) * w * gate(g)                  (the gate follows the norm)
 // w has C entries, or C / groups entries shared by the parts (w_shared).  One block per row.
+// A part of y spans y_gs >= C / groups numbers (the rest is skipped), except with `stab`: then number C / groups of every
+// part is a normaliser's product nq and stab[m][part] a stabiliser mx, and the part is first divided by
+// max(|nq|, exp(-mx)) + 1e-6 (the read-out of a matrix memory with exponential gates).
 template <typename TA>
-__global__ void gated_group_norm_kernel(const float* __restrict__ y, const TA* __restrict__ gate, int gate_stride,
-                                        const float* __restrict__ w, int w_shared, float eps, int groups, int gate_first,
-                                        TA* __restrict__ out, int C) {
+__global__ void gated_group_norm_kernel(const float* __restrict__ y, int y_gs, const float* __restrict__ stab,
+                                        const TA* __restrict__ gate, int gate_stride, const float* __restrict__ w, int w_shared,
+                                        float eps, int groups, int gate_first, int gate_sigmoid, TA* __restrict__ out, int C) {
   const int m = blockIdx.x;
   const int gs = C / groups;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
   for (int g = warp; g < groups; g += nw) {
-    const float* yr = y + (size_t)m * C + (size_t)g * gs;
+    const float* yr = y + ((size_t)m * groups + g) * y_gs;
     const TA* gr = gate + (size_t)m * gate_stride + (size_t)g * gs;
+    const float pre = stab ? 1.f / (fmaxf(fabsf(yr[gs]), expf(-stab[(size_t)m * groups + g])) + 1e-6f) : 1.f;
     float ss = 0.f;
     for (int i = lane; i < gs; i += 32) {
-      float v = yr[i];
+      float v = yr[i] * pre;
       if (gate_first) {
         const float z = dt<TA>::ld(gr, i);
-        v *= z / (1.f + expf(-z));
+        v *= (gate_sigmoid ? 1.f : z) / (1.f + expf(-z));
       }
       ss += v * v;
     }
@@ -223,9 +228,10 @@ __global__ void gated_group_norm_kernel(const float* __restrict__ y, const TA* _
     const float k = 1.f / sqrtf(ss / (float)gs + eps);
     for (int i = lane; i < gs; i += 32) {
       const float z = dt<TA>::ld(gr, i);
-      const float sg = z / (1.f + expf(-z));
+      const float sg = (gate_sigmoid ? 1.f : z) / (1.f + expf(-z));
       const float wv = w[w_shared ? i : g * gs + i];
-      const float v = gate_first ? (yr[i] * sg) * k * wv : yr[i] * k * wv * sg;
+      const float yv = yr[i] * pre;
+      const float v = gate_first ? (yv * sg) * k * wv : yv * k * wv * sg;
       dt<TA>::st(out, (size_t)m * C + (size_t)g * gs + i, v);
     }
   }
@@ -238,6 +244,17 @@ __global__ void relu_squared_kernel(T* __restrict__ h, size_t n) {
   if (i >= n) return;
   const float v = fmaxf(dt<T>::ld(h, i), 0.f);
   dt<T>::st(h, i, v * v);
+}
+
+// in place: gelu(v), the erf form 0.5 v (1 + erf(v / sqrt 2)) or (tanh_form) 0.5 v (1 + tanh(sqrt(2/pi) (v + 0.044715 v^3)))
+template <typename T>
+__global__ void gelu_kernel(T* __restrict__ h, int tanh_form, size_t n) {
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const float v = dt<T>::ld(h, i);
+  const float r = tanh_form ? 0.5f * v * (1.f + tanhf(0.7978845608028654f * (v + 0.044715f * v * v * v)))
+                            : 0.5f * v * (1.f + erff(v * 0.7071067811865476f));
+  dt<T>::st(h, i, r);
 }
 
 }  // namespace llb
@@ -266,19 +283,22 @@ int ll_add_norm_pair(float* x, const void* a0, float s0, const void* a1, float s
   return LL_OK;
 }
 
-int ll_gated_group_norm(const float* y, const void* gate, int gate_stride, const float* w, int w_shared, float eps, int groups,
-                        int gate_first, void* out, int act_dtype, int rows, int C, ll_stream stream) {
+int ll_gated_group_norm(const float* y, int y_gs, const float* stab, const void* gate, int gate_stride, const float* w, int w_shared,
+                        float eps, int groups, int gate_first, int gate_sigmoid, void* out, int act_dtype, int rows, int C,
+                        ll_stream stream) {
   LL_CHECK_ARG(y && gate && w && out && rows >= 0 && C > 0 && groups > 0 && C % groups == 0 && gate_stride >= C,
                "bad gated_group_norm arguments");
+  if (y_gs == 0) y_gs = C / groups;
+  LL_CHECK_ARG(y_gs >= C / groups + (stab ? 1 : 0), "gated_group_norm: a part of y is shorter than the part it norms");
   if (rows == 0) return LL_OK;
   cudaStream_t st = (cudaStream_t)stream;
   const int threads = groups >= 8 ? 256 : groups >= 4 ? 128 : 32 * groups;
   if (act_dtype == LL_F32)
-    gated_group_norm_kernel<float><<<rows, threads, 0, st>>>(y, (const float*)gate, gate_stride, w, w_shared, eps, groups, gate_first,
-                                                            (float*)out, C);
+    gated_group_norm_kernel<float><<<rows, threads, 0, st>>>(y, y_gs, stab, (const float*)gate, gate_stride, w, w_shared, eps, groups,
+                                                            gate_first, gate_sigmoid, (float*)out, C);
   else if (act_dtype == LL_BF16)
-    gated_group_norm_kernel<__nv_bfloat16><<<rows, threads, 0, st>>>(y, (const __nv_bfloat16*)gate, gate_stride, w, w_shared, eps,
-                                                                    groups, gate_first, (__nv_bfloat16*)out, C);
+    gated_group_norm_kernel<__nv_bfloat16><<<rows, threads, 0, st>>>(y, y_gs, stab, (const __nv_bfloat16*)gate, gate_stride, w, w_shared,
+                                                                    eps, groups, gate_first, gate_sigmoid, (__nv_bfloat16*)out, C);
   else {
     set_error("gated_group_norm: unsupported dtype %d", act_dtype);
     return LL_ERR_UNSUPPORTED;
@@ -299,6 +319,21 @@ int ll_relu_squared(void* h, int dtype, size_t n, ll_stream stream) {
     return LL_ERR_UNSUPPORTED;
   }
   LL_LAUNCH_OK("relu_squared_kernel");
+  return LL_OK;
+}
+
+int ll_gelu(void* h, int dtype, int tanh_form, size_t n, ll_stream stream) {
+  LL_CHECK_ARG(h, "gelu: null pointer");
+  if (n == 0) return LL_OK;
+  cudaStream_t st = (cudaStream_t)stream;
+  const unsigned blocks = (unsigned)((n + 255) / 256);
+  if (dtype == LL_F32) gelu_kernel<float><<<blocks, 256, 0, st>>>((float*)h, tanh_form, n);
+  else if (dtype == LL_BF16) gelu_kernel<__nv_bfloat16><<<blocks, 256, 0, st>>>((__nv_bfloat16*)h, tanh_form, n);
+  else {
+    set_error("gelu: unsupported dtype %d", dtype);
+    return LL_ERR_UNSUPPORTED;
+  }
+  LL_LAUNCH_OK("gelu_kernel");
   return LL_OK;
 }
 

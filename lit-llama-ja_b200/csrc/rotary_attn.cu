@@ -1,0 +1,374 @@
+// Softmax attention with rotary positions over a ring of key / value rows, with the variations as parameters:
+//
+//   prepare   q, k <- [rmsnorm over the WHOLE projection row * w]  ->  rotation of the first `rot_dims` dimensions of every head
+//             (dimension i paired with i + rot_dims/2, angle = position * freq[i], all fp32)  ->  q rows out, k rows into the
+//             ring at slot position % ring; the value rows are a projection of their own or the keys BEFORE rotation.
+//   attend    s_h(i, j) = scale * q_h(i).k_g(j),  optionally cap * tanh(s / cap);
+//             key j visible to query i when j <= i, (window == 0 or i - j < window), (chunk == 0 or j / chunk == i / chunk);
+//             softmax over the visible keys, optionally with exp(sink_h) added to the denominator (a key without a value);
+//             o_h(i) = sum_j w(i, j) v_g(j), optionally times sigmoid(gate) element by element.
+//
+// Query head h reads key / value head g = h / (H / G).  Scores, softmax and the weighted sums are fp32 in every form; the
+// tensor-core form (prompts in bf16) rounds the softmax weights to bf16 as the operand of P.V, which is the only place.
+#include "common.cuh"
+
+namespace llb {
+
+// ---------------------------------------------------------------------------------------------------------------- prepare
+constexpr int QP_THREADS = 256;
+
+__device__ __forceinline__ float qp_block_sum(float v, float* red) {
+  v = warp_sum(v);
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  if (lane == 0) red[w] = v;
+  __syncthreads();
+  float t = (threadIdx.x < nw) ? red[threadIdx.x] : 0.f;
+  if (w == 0) {
+    t = warp_sum(t);
+    if (lane == 0) red[0] = t;
+  }
+  __syncthreads();
+  t = red[0];
+  __syncthreads();
+  return t;
+}
+
+// One row of `heads` heads of `dim`: optional whole-row norm, rotation, store to `out` (row of heads * dim); `plain`
+// (optional) gets the row as it is before the rotation (after the norm).
+template <typename T>
+__device__ __forceinline__ void qp_row(const T* __restrict__ x, const float* __restrict__ nw, float eps, const float* __restrict__ freq,
+                                       int rot_dims, float pos, int heads, int dim, T* __restrict__ out, T* __restrict__ plain,
+                                       float* red) {
+  const int n = heads * dim, half = rot_dims >> 1;
+  float kn = 1.f;
+  if (nw) {
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+      const float v = dt<T>::ld(x, i);
+      ss += v * v;
+    }
+    ss = qp_block_sum(ss, red);
+    kn = 1.f / sqrtf(ss / (float)n + eps);
+  }
+  for (int idx = threadIdx.x; idx < n; idx += blockDim.x) {
+    const int i = idx % dim;
+    float a = dt<T>::ld(x, idx) * kn;
+    if (nw) a *= nw[idx];
+    if (plain) dt<T>::st(plain, idx, a);
+    if (i < rot_dims) {
+      const bool lower = i < half;
+      const int mate = lower ? idx + half : idx - half;
+      float b = dt<T>::ld(x, mate) * kn;
+      if (nw) b *= nw[mate];
+      float sn, cs;
+      sincosf(pos * freq[lower ? i : i - half], &sn, &cs);
+      a = lower ? a * cs - b * sn : a * cs + b * sn;
+    }
+    dt<T>::st(out, idx, a);
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(QP_THREADS) qk_rotary_append_kernel(
+    const T* __restrict__ q, int q_stride, const T* __restrict__ k, int k_stride, const T* __restrict__ v, int v_stride,
+    const float* __restrict__ q_norm, const float* __restrict__ k_norm, float eps, const float* __restrict__ freq, int rot_dims,
+    const int32_t* __restrict__ pos_ids, T* __restrict__ q_out, T* __restrict__ kc, T* __restrict__ vc, int Tn, int H, int G, int dim,
+    int vdim, int ring) {
+  __shared__ float red[32];
+  const int m = blockIdx.x, b = m / Tn, t = m - b * Tn;
+  const int p = pos_ids[t];
+  const float pos = (float)p;
+  qp_row<T>(q + (size_t)m * q_stride, q_norm, eps, freq, rot_dims, pos, H, dim, q_out + (size_t)m * H * dim, nullptr, red);
+  if (!k) return;
+  const size_t slot = (size_t)b * ring + (size_t)(p % ring);
+  T* vrow = vc + slot * (size_t)G * vdim;
+  qp_row<T>(k + (size_t)m * k_stride, k_norm, eps, freq, rot_dims, pos, G, dim, kc + slot * (size_t)G * dim, v ? nullptr : vrow, red);
+  if (v)
+    for (int i = threadIdx.x; i < G * vdim; i += blockDim.x) vrow[i] = v[(size_t)m * v_stride + i];
+}
+
+// ---------------------------------------------------------------------------------------------------------------- attend, fp32 form
+// A warp owns one (query, head); its four groups of eight lanes take every fourth visible key, the eight lanes of a group
+// split the head's dimensions in runs of eight (one 16-byte load in bf16).  Every group keeps a running (max, sum, weighted
+// sum); the groups are merged at the end.  With splits > 1 a query's keys are cut into that many ranges (blockIdx.y), each
+// leaving its (max, sum, weighted sum) in scratch for the merge kernel: decoding one token over a long cache then fills the
+// device.
+constexpr int SA_WARPS = 4;
+
+template <typename T>
+__device__ __forceinline__ void sa_load8(const T* __restrict__ row, int e0, int n, bool vec, float (&o)[8]);
+template <>
+__device__ __forceinline__ void sa_load8<float>(const float* __restrict__ row, int e0, int n, bool vec, float (&o)[8]) {
+  if (vec && e0 + 8 <= n) {
+    const float4 a = *(const float4*)(row + e0), b = *(const float4*)(row + e0 + 4);
+    o[0] = a.x, o[1] = a.y, o[2] = a.z, o[3] = a.w, o[4] = b.x, o[5] = b.y, o[6] = b.z, o[7] = b.w;
+  } else {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) o[i] = e0 + i < n ? row[e0 + i] : 0.f;
+  }
+}
+template <>
+__device__ __forceinline__ void sa_load8<__nv_bfloat16>(const __nv_bfloat16* __restrict__ row, int e0, int n, bool vec, float (&o)[8]) {
+  if (vec && e0 + 8 <= n) {
+    const uint4 u = *(const uint4*)(row + e0);
+    o[0] = bf16_bits_to_f32(u.x & 0xffffu), o[1] = bf16_bits_to_f32(u.x >> 16);
+    o[2] = bf16_bits_to_f32(u.y & 0xffffu), o[3] = bf16_bits_to_f32(u.y >> 16);
+    o[4] = bf16_bits_to_f32(u.z & 0xffffu), o[5] = bf16_bits_to_f32(u.z >> 16);
+    o[6] = bf16_bits_to_f32(u.w & 0xffffu), o[7] = bf16_bits_to_f32(u.w >> 16);
+  } else {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) o[i] = e0 + i < n ? __bfloat162float(row[e0 + i]) : 0.f;
+  }
+}
+
+__device__ __forceinline__ int sa_first_visible(int i, int window, int chunk) {
+  int lo = 0;
+  if (window > 0) lo = max(lo, i - window + 1);
+  if (chunk > 0) lo = max(lo, (i / chunk) * chunk);
+  return lo;
+}
+
+// R / RV: runs of 64 dimensions a head's keys / values span (dim <= 64 R, vdim <= 64 RV).
+template <typename T, int R, int RV>
+__global__ void __launch_bounds__(SA_WARPS * 32) softmax_attn_kernel(
+    const T* __restrict__ q, int q_stride, const T* __restrict__ gate, int gate_stride, const T* __restrict__ kc, const T* __restrict__ vc,
+    const int32_t* __restrict__ pos_ids, const float* __restrict__ sink, float scale, float softcap, int Tn, int H, int G, int dim,
+    int vdim, int window, int chunk, int ring, int splits, int pairs, float* __restrict__ part_ml, float* __restrict__ part_acc,
+    T* __restrict__ y) {
+  const int pair = blockIdx.x * SA_WARPS + (threadIdx.x >> 5);
+  if (pair >= pairs) return;
+  const int lane = threadIdx.x & 31, grp = lane >> 3, sub = lane & 7;
+  const int m = pair / H, h = pair - m * H, g = h / (H / G);
+  const int b = m / Tn, t = m - b * Tn;
+  const int i = pos_ids[t];
+  const int lo = sa_first_visible(i, window, chunk);
+  const int nvis = i - lo + 1;
+  const int per = (nvis + splits - 1) / splits;
+  const int j0 = lo + blockIdx.y * per, j1 = min(i + 1, j0 + per);
+  const bool kvec = (dim & 7) == 0, vvec = (vdim & 7) == 0;
+  float qr[R][8];
+  const T* qrow = q + (size_t)m * q_stride + (size_t)h * dim;
+#pragma unroll
+  for (int r = 0; r < R; ++r) sa_load8<T>(qrow, r * 64 + sub * 8, dim, kvec && ((q_stride | (h * dim)) & 7) == 0, qr[r]);
+  float acc[RV][8];
+#pragma unroll
+  for (int r = 0; r < RV; ++r)
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc[r][e] = 0.f;
+  float mx = -INFINITY, l = 0.f;
+  const float inv_cap = softcap > 0.f ? 1.f / softcap : 0.f;
+  const T* kbase = kc + ((size_t)b * ring * G + g) * dim;
+  const T* vbase = vc + ((size_t)b * ring * G + g) * vdim;
+  const unsigned gmask = 0xffu << (grp * 8);
+  for (int j = j0 + grp; j < j1; j += 4) {
+    const size_t slot = (size_t)(j % ring);
+    const T* krow = kbase + slot * G * dim;
+    float s = 0.f;
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      float kk[8];
+      sa_load8<T>(krow, r * 64 + sub * 8, dim, kvec, kk);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) s = fmaf(qr[r][e], kk[e], s);
+    }
+    s += __shfl_xor_sync(gmask, s, 1);          // the groups' trip counts differ: only the group's own lanes meet here
+    s += __shfl_xor_sync(gmask, s, 2);
+    s += __shfl_xor_sync(gmask, s, 4);
+    s *= scale;
+    if (softcap > 0.f) s = softcap * tanhf(s * inv_cap);
+    const float mn = fmaxf(mx, s);
+    const float corr = expf(mx - mn), p = expf(s - mn);
+    mx = mn;
+    l = l * corr + p;
+    const T* vrow = vbase + slot * G * vdim;
+#pragma unroll
+    for (int r = 0; r < RV; ++r) {
+      float vv[8];
+      sa_load8<T>(vrow, r * 64 + sub * 8, vdim, vvec, vv);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc[r][e] = fmaf(p, vv[e], acc[r][e] * corr);
+    }
+  }
+  // the four groups of the warp hold disjoint keys: merge them (lanes 8 and 16 apart hold the same dimensions).  The
+  // trip counts differ between groups, so the shuffles wait until the whole warp is here.
+  __syncwarp();
+#pragma unroll
+  for (int o = 8; o <= 16; o <<= 1) {
+    const float m2 = __shfl_xor_sync(0xffffffffu, mx, o), l2 = __shfl_xor_sync(0xffffffffu, l, o);
+    const float mn = fmaxf(mx, m2);
+    const float c1 = mx == -INFINITY ? 0.f : expf(mx - mn), c2 = m2 == -INFINITY ? 0.f : expf(m2 - mn);
+    l = l * c1 + l2 * c2;
+#pragma unroll
+    for (int r = 0; r < RV; ++r)
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        const float a2 = __shfl_xor_sync(0xffffffffu, acc[r][e], o);
+        acc[r][e] = acc[r][e] * c1 + a2 * c2;
+      }
+    mx = mn;
+  }
+  if (splits > 1) {
+    const size_t at = (size_t)pair * splits + blockIdx.y;
+    if (lane == 0) part_ml[at * 2] = mx, part_ml[at * 2 + 1] = l;
+    if (grp == 0) {
+#pragma unroll
+      for (int r = 0; r < RV; ++r)
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          const int c = r * 64 + sub * 8 + e;
+          if (c < vdim) part_acc[at * vdim + c] = acc[r][e];
+        }
+    }
+    return;
+  }
+  if (grp != 0) return;
+  float den = l;
+  if (sink) {
+    const float sk = sink[h];
+    const float mn = fmaxf(mx, sk);
+    const float c1 = expf(mx - mn);
+    den = l * c1 + expf(sk - mn);
+#pragma unroll
+    for (int r = 0; r < RV; ++r)
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc[r][e] *= c1;
+  }
+  const float inv = 1.f / den;
+#pragma unroll
+  for (int r = 0; r < RV; ++r)
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      const int c = r * 64 + sub * 8 + e;
+      if (c < vdim) {
+        float o = acc[r][e] * inv;
+        if (gate) o *= 1.f / (1.f + expf(-dt<T>::ld(gate, (size_t)m * gate_stride + (size_t)h * vdim + c)));
+        dt<T>::st(y, (size_t)m * H * vdim + (size_t)h * vdim + c, o);
+      }
+    }
+}
+
+// Merge of the key ranges of one (query, head), in order; a warp per pair, a lane per value dimension.
+template <typename T>
+__global__ void softmax_attn_merge_kernel(const float* __restrict__ part_ml, const float* __restrict__ part_acc,
+                                          const T* __restrict__ gate, int gate_stride, const float* __restrict__ sink, int H, int vdim,
+                                          int splits, int pairs, T* __restrict__ y) {
+  const int pair = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (pair >= pairs) return;
+  const int lane = threadIdx.x & 31;
+  const int m = pair / H, h = pair - m * H;
+  float mx = sink ? sink[h] : -INFINITY;
+  for (int s = 0; s < splits; ++s) mx = fmaxf(mx, part_ml[((size_t)pair * splits + s) * 2]);
+  float den = sink ? expf(sink[h] - mx) : 0.f;
+  for (int s = 0; s < splits; ++s) {
+    const float ms = part_ml[((size_t)pair * splits + s) * 2];
+    if (ms != -INFINITY) den += part_ml[((size_t)pair * splits + s) * 2 + 1] * expf(ms - mx);
+  }
+  const float inv = 1.f / den;
+  for (int c = lane; c < vdim; c += 32) {
+    float o = 0.f;
+    for (int s = 0; s < splits; ++s) {
+      const float ms = part_ml[((size_t)pair * splits + s) * 2];
+      if (ms != -INFINITY) o += part_acc[((size_t)pair * splits + s) * vdim + c] * expf(ms - mx);
+    }
+    o *= inv;
+    if (gate) o *= 1.f / (1.f + expf(-dt<T>::ld(gate, (size_t)m * gate_stride + (size_t)h * vdim + c)));
+    dt<T>::st(y, (size_t)m * H * vdim + (size_t)h * vdim + c, o);
+  }
+}
+
+template <typename T, int R, int RV>
+static int sa_launch(const void* q, int q_stride, const void* gate, int gate_stride, const void* kc, const void* vc,
+                     const int32_t* pos_ids, const float* sink, float scale, float softcap, int B, int Tn, int H, int G, int dim,
+                     int vdim, int window, int chunk, int ring, int splits, float* scratch, void* y, cudaStream_t st) {
+  const int pairs = B * Tn * H;
+  float* part_ml = scratch;
+  float* part_acc = scratch ? scratch + (size_t)pairs * splits * 2 : nullptr;
+  const dim3 grid((pairs + SA_WARPS - 1) / SA_WARPS, splits);
+  softmax_attn_kernel<T, R, RV><<<grid, SA_WARPS * 32, 0, st>>>((const T*)q, q_stride, (const T*)gate, gate_stride, (const T*)kc,
+                                                               (const T*)vc, pos_ids, sink, scale, softcap, Tn, H, G, dim, vdim, window,
+                                                               chunk, ring, splits, pairs, part_ml, part_acc, (T*)y);
+  LL_LAUNCH_OK("softmax_attn_kernel");
+  if (splits > 1) {
+    softmax_attn_merge_kernel<T><<<(pairs + 3) / 4, 128, 0, st>>>(part_ml, part_acc, (const T*)gate, gate_stride, sink, H, vdim, splits,
+                                                                 pairs, (T*)y);
+    LL_LAUNCH_OK("softmax_attn_merge_kernel");
+  }
+  return LL_OK;
+}
+
+template <typename T>
+static int sa_dispatch(const void* q, int q_stride, const void* gate, int gate_stride, const void* kc, const void* vc,
+                       const int32_t* pos_ids, const float* sink, float scale, float softcap, int B, int Tn, int H, int G, int dim,
+                       int vdim, int window, int chunk, int ring, int splits, float* scratch, void* y, cudaStream_t st) {
+  const int r = dim <= 64 ? 1 : dim <= 128 ? 2 : 4, rv = vdim <= 64 ? 1 : vdim <= 128 ? 2 : 4;
+#define LL_SA(RR, RRV)                                                                                                              \
+  if (r == RR && rv == RRV)                                                                                                         \
+    return sa_launch<T, RR, RRV>(q, q_stride, gate, gate_stride, kc, vc, pos_ids, sink, scale, softcap, B, Tn, H, G, dim, vdim, window, \
+                                 chunk, ring, splits, scratch, y, st);
+  LL_SA(1, 1) LL_SA(1, 2) LL_SA(1, 4) LL_SA(2, 1) LL_SA(2, 2) LL_SA(2, 4) LL_SA(4, 1) LL_SA(4, 2) LL_SA(4, 4)
+#undef LL_SA
+  return LL_ERR_UNSUPPORTED;
+}
+
+}  // namespace llb
+
+using namespace llb;
+
+extern "C" {
+
+int ll_qk_rotary_append(const void* q, int q_stride, const void* k, int k_stride, const void* v, int v_stride, int dtype,
+                        const float* q_norm, const float* k_norm, float eps, const float* freq, int rot_dims,
+                        const int32_t* pos_ids, void* q_out, void* kc, void* vc, int B, int T, int H, int G, int dim, int vdim, int ring,
+                        ll_stream stream) {
+  LL_CHECK_ARG(q && q_out && pos_ids && B >= 0 && T >= 0 && H > 0 && dim > 0, "bad qk_rotary_append arguments");
+  LL_CHECK_ARG(rot_dims >= 0 && rot_dims <= dim && rot_dims % 2 == 0 && (rot_dims == 0 || freq), "qk_rotary_append: bad rotation");
+  LL_CHECK_ARG(!k || (kc && vc && G > 0 && vdim > 0 && ring > 0), "qk_rotary_append: keys need their ring");
+  LL_CHECK_ARG(!k || v || vdim == dim, "qk_rotary_append: values taken from the keys have the keys' size");
+  if (B == 0 || T == 0) return LL_OK;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (dtype == LL_F32)
+    qk_rotary_append_kernel<float><<<B * T, QP_THREADS, 0, st>>>((const float*)q, q_stride, (const float*)k, k_stride, (const float*)v,
+                                                                v_stride, q_norm, k_norm, eps, freq, rot_dims, pos_ids, (float*)q_out,
+                                                                (float*)kc, (float*)vc, T, H, G, dim, vdim, ring);
+  else if (dtype == LL_BF16)
+    qk_rotary_append_kernel<__nv_bfloat16><<<B * T, QP_THREADS, 0, st>>>(
+        (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)k, k_stride, (const __nv_bfloat16*)v, v_stride, q_norm, k_norm, eps,
+        freq, rot_dims, pos_ids, (__nv_bfloat16*)q_out, (__nv_bfloat16*)kc, (__nv_bfloat16*)vc, T, H, G, dim, vdim, ring);
+  else {
+    set_error("qk_rotary_append: unsupported dtype %d", dtype);
+    return LL_ERR_UNSUPPORTED;
+  }
+  LL_LAUNCH_OK("qk_rotary_append_kernel");
+  return LL_OK;
+}
+
+size_t ll_softmax_attn_scratch_bytes(int M, int H, int vdim, int splits) {
+  if (splits <= 1) return 16;
+  return (size_t)M * H * splits * (2 + (size_t)vdim) * sizeof(float);
+}
+
+int ll_softmax_attn(const void* q, int q_stride, const void* gate, int gate_stride, const void* kc, const void* vc, int dtype,
+                    const int32_t* pos_ids, const float* sink, float scale, float softcap, int B, int T, int H, int G, int dim,
+                    int vdim, int window, int chunk, int ring, int splits, int form, float* scratch, void* y, ll_stream stream) {
+  LL_CHECK_ARG(q && kc && vc && pos_ids && y, "softmax_attn: null pointer");
+  LL_CHECK_ARG(B >= 0 && T >= 0 && H > 0 && G > 0 && H % G == 0 && dim > 0 && vdim > 0 && ring > 0 && window >= 0 && chunk >= 0 &&
+                   splits >= 1 && (splits == 1 || scratch),
+               "bad softmax_attn arguments");
+  if (dim > 256 || vdim > 256) {
+    set_error("softmax_attn: heads of %d / %d dimensions (up to 256)", dim, vdim);
+    return LL_ERR_UNSUPPORTED;
+  }
+  if (B == 0 || T == 0) return LL_OK;
+  cudaStream_t st = (cudaStream_t)stream;
+  (void)form;
+  if (dtype == LL_F32)
+    return sa_dispatch<float>(q, q_stride, gate, gate_stride, kc, vc, pos_ids, sink, scale, softcap, B, T, H, G, dim, vdim, window, chunk,
+                              ring, splits, scratch, y, st);
+  if (dtype == LL_BF16)
+    return sa_dispatch<__nv_bfloat16>(q, q_stride, gate, gate_stride, kc, vc, pos_ids, sink, scale, softcap, B, T, H, G, dim, vdim, window,
+                                      chunk, ring, splits, scratch, y, st);
+  set_error("softmax_attn: unsupported dtype %d", dtype);
+  return LL_ERR_UNSUPPORTED;
+}
+
+}  // extern "C"

@@ -122,11 +122,18 @@ EXPORTS = {
     "ll_moe_tc_error": ([], C.c_int),
     "ll_moe_combine": ([vp, vp, i32, vp, i32, vp, i32, vp, i32, i32, i32, vp], C.c_int),
     "ll_add_norm_pair": ([vp, vp, C.c_float, vp, C.c_float, vp, C.c_float, vp, vp, C.c_float, vp, i32, vp, i32, i32, i32, vp], C.c_int),
-    "ll_gated_group_norm": ([vp, vp, i32, vp, i32, C.c_float, i32, i32, vp, i32, i32, i32, vp], C.c_int),
+    "ll_gated_group_norm": ([vp, i32, vp, vp, i32, vp, i32, C.c_float, i32, i32, i32, vp, i32, i32, i32, vp], C.c_int),
+    "ll_gelu": ([vp, i32, i32, sz_t, vp], C.c_int),
     "ll_relu_squared": ([vp, i32, sz_t, vp], C.c_int),
     "ll_short_conv": ([vp, i32, i32, i32, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, vp], C.c_int),
-    "ll_decay_scan": ([vp, i32, vp, i32, vp, i32, i32, vp, i32, vp, vp, C.c_float, vp, vp, vp, i32, i32, i32, i32, i32, i32, vp],
+    "ll_decay_scan": ([vp, i32, vp, i32, vp, i32, i32, vp, i32, vp, vp, C.c_float, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, vp],
                       C.c_int),
+    "ll_matrix_memory_gates": ([vp, vp, i32, i32, vp, vp, C.c_float, vp, vp, vp, vp, vp, i32, i32, i32, vp], C.c_int),
+    "ll_qk_rotary_append": ([vp, i32, vp, i32, vp, i32, i32, vp, vp, C.c_float, vp, i32, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32,
+                             i32, vp], C.c_int),
+    "ll_softmax_attn_scratch_bytes": ([i32, i32, i32, i32], sz_t),
+    "ll_softmax_attn": ([vp, i32, vp, i32, vp, vp, i32, vp, vp, C.c_float, C.c_float, i32, i32, i32, i32, i32, i32, i32, i32, i32,
+                         i32, i32, vp, vp, vp], C.c_int),
     "ll_ssm_gates": ([vp, i32, i32, vp, vp, vp, vp, i32, i32, vp], C.c_int),
     "ll_channel_decay": ([vp, i32, i32, vp, C.c_float, vp, i32, i32, vp], C.c_int),
     "ll_sink_ring_append": ([vp, i32, vp, i32, i32, vp, vp, vp, i32, i32, i32, i32, i32, i32, vp], C.c_int),
@@ -136,7 +143,7 @@ EXPORTS = {
 }
 _fn = {name: _proto(name, a, r) for name, (a, r) in EXPORTS.items()}
 
-ABI_VERSION = 13
+ABI_VERSION = 14
 if _fn["ll_abi_version"]() != ABI_VERSION:
     raise ImportError("libllb200.so ABI version mismatch; rebuild with lit-llama-ja_b200/build.py")
 

@@ -9,11 +9,11 @@ from . import _native as N
 
 
 class DenseFF(nn.Module):
-    """``act``: "relu2" (the square of relu)."""
+    """``act``: "relu2" (the square of relu), "gelu" (the erf form) or "gelu_tanh"."""
 
     def __init__(self, width: int, ff: int, act: str, dtype: torch.dtype, device) -> None:
         super().__init__()
-        if act != "relu2":
+        if act not in ("relu2", "gelu", "gelu_tanh"):
             raise ValueError(f"unknown feed-forward activation {act!r}")
         self.act = act
         kw = dict(dtype=dtype, device=device)
@@ -26,5 +26,8 @@ class DenseFF(nn.Module):
 
     def forward(self, x_act: torch.Tensor) -> torch.Tensor:
         h = F.linear(x_act, self.w_up)
-        N.call("ll_relu_squared", N.ptr(h), N.dtype_code(h.dtype), h.numel(), N.stream())
+        if self.act == "relu2":
+            N.call("ll_relu_squared", N.ptr(h), N.dtype_code(h.dtype), h.numel(), N.stream())
+        else:
+            N.call("ll_gelu", N.ptr(h), N.dtype_code(h.dtype), 1 if self.act == "gelu_tanh" else 0, h.numel(), N.stream())
         return F.linear(h, self.w_down)

@@ -7,6 +7,12 @@
 * ``GatedLinearAttention`` - a decay per key channel:
       alpha = sigmoid(W_a2 W_a1 h + b)^(1/tau);  S_t = diag(alpha_t) S_(t-1) + k_t v_t^T;  o_t = S_t^T q_t * dim^(-1/2)
       out = W_o ( headnorm(o) * w * silu(W_g h) )
+* ``MatrixMemoryMixer`` - matrix memory with exponential gates ("mLSTM" form): log gates li = cap(W_i h + b_i),
+  lf = logsigmoid(cap(W_f h + b_f)), cap(z) = c tanh(z / c), and a running stabiliser mx (0 at the start):
+      mx_t = max(lf_t + mx_(t-1), li_t);  S_t = e^(lf_t + mx_(t-1) - mx_t) S_(t-1) + e^(li_t - mx_t) k_t v_t^T;  n_t alike with k_t alone
+      o_t = S_t^T q_t / (max(|n_t . q_t|, e^(-mx_t)) + 1e-6),  q_t = W_q h * dim^(-1/2)
+      out = W_o ( headnorm(o) * w * sigmoid(W_g h) )
+  The normaliser n rides in the same walk as one more value column that is constantly 1.
 
 Decays, step sizes, the state, the read-out and the norms are fp32; the projections, the short convolution's output and
 the gates are in the activation dtype.  A sequence at position 0 starts from a zero state whatever its slot holds.
@@ -28,19 +34,25 @@ def pad8(n: int) -> int:
     return (n + 7) // 8 * 8
 
 
-def decay_scan(q, q_col, k, k_col, v, v_col, decay, per_channel, kscale, skip, qscale, state, pos_ids, B, T, H, qk_heads, n, p):
-    """fp32 ``[B*T, H*p]``: the read-out of the recurrence (see csrc/decay_scan.cu); ``state`` is advanced in place."""
+def decay_scan(q, q_col, k, k_col, v, v_col, decay, per_channel, kscale, skip, qscale, state, pos_ids, B, T, H, qk_heads, n, p,
+               unit_col=False):
+    """fp32 ``[B*T, H*p]``: the read-out of the recurrence (see csrc/decay_scan.cu); ``state`` is advanced in place.
+    ``unit_col``: the last of the ``p`` columns of every head is the constant 1 (``v`` holds ``p - 1`` per head)."""
     y = torch.empty((B * T, H * p), dtype=torch.float32, device=v.device)
     N.call("ll_decay_scan", N.ptr_at(q, q_col), q.stride(0), N.ptr_at(k, k_col), k.stride(0), N.ptr_at(v, v_col), v.stride(0),
            N.dtype_code(v.dtype), N.ptr(decay), 1 if per_channel else 0, N.ptr(kscale), N.ptr(skip), float(qscale), N.ptr(state),
-           N.ptr(pos_ids), N.ptr(y), B, T, H, qk_heads, n, p, N.stream())
+           N.ptr(pos_ids), N.ptr(y), B, T, H, qk_heads, n, p, 1 if unit_col else 0, N.stream())
     return y
 
 
-def gated_group_norm(y, gate, gate_col, weight, shared, eps, groups, gate_first, out_dtype):
-    out = torch.empty(y.shape, dtype=out_dtype, device=y.device)
-    N.call("ll_gated_group_norm", N.ptr(y), N.ptr_at(gate, gate_col), gate.stride(0), N.ptr(weight), 1 if shared else 0, float(eps),
-           groups, 1 if gate_first else 0, N.ptr(out), N.dtype_code(out_dtype), y.shape[0], y.shape[1], N.stream())
+def gated_group_norm(y, gate, gate_col, weight, shared, eps, groups, gate_first, out_dtype, sigmoid=False, part=None, stab=None):
+    """``y`` fp32 ``[rows, groups * part]`` (``part`` None: the parts are what is normed, nothing between them); see
+    csrc/residual_ops.cu for ``stab``."""
+    C = y.shape[1] if part is None else groups * part
+    out = torch.empty((y.shape[0], C), dtype=out_dtype, device=y.device)
+    N.call("ll_gated_group_norm", N.ptr(y), y.shape[1] // groups, N.ptr(stab), N.ptr_at(gate, gate_col), gate.stride(0), N.ptr(weight),
+           1 if shared else 0, float(eps), groups, 1 if gate_first else 0, 1 if sigmoid else 0, N.ptr(out), N.dtype_code(out_dtype),
+           y.shape[0], C, N.stream())
     return out
 
 
@@ -170,4 +182,60 @@ class GatedLinearAttention(nn.Module):
         y = decay_scan(proj, col0 + c["q"], proj, col0 + c["k"], proj, col0 + c["v"], alpha, True, None, None, s.dim ** -0.5,
                        states[0], pos_ids, B, T, s.heads, s.heads, s.dim, s.vdim)
         out = gated_group_norm(y, proj, col0 + c["g"], self.norm, True, s.eps, s.heads, False, proj.dtype)
+        return F.linear(out, self.w_o)
+
+
+@dataclass
+class MatrixMemorySpec:
+    width: int
+    heads: int
+    dim: int                # query / key channels per head
+    vdim: int
+    gate_cap: float         # 0: the gates' pre-activations are not capped
+    eps: float
+
+
+class MatrixMemoryMixer(nn.Module):
+    def __init__(self, spec: MatrixMemorySpec, dtype: torch.dtype, device) -> None:
+        super().__init__()
+        s = self.spec = spec
+        kw = dict(dtype=dtype, device=device)
+        f32 = dict(dtype=torch.float32, device=device)
+        hd, hv = s.heads * s.dim, s.heads * s.vdim
+        self.cols = dict(q=0, k=hd, v=2 * hd, g=2 * hd + hv, i=2 * hd + 2 * hv, f=2 * hd + 2 * hv + s.heads)
+        self.n_in = 2 * hd + 2 * hv + 2 * s.heads
+        self.w_in = nn.Parameter(torch.zeros((pad8(self.n_in), s.width), **kw), requires_grad=False)
+        self.bias_i = nn.Parameter(torch.zeros(s.heads, **f32), requires_grad=False)
+        self.bias_f = nn.Parameter(torch.zeros(s.heads, **f32), requires_grad=False)
+        self.norm = nn.Parameter(torch.ones(hv, **f32), requires_grad=False)
+        self.w_o = nn.Parameter(torch.zeros((s.width, hv), **kw), requires_grad=False)
+
+    def state_shapes(self, B: int) -> List[Tuple[int, ...]]:
+        """fp32: the memory with its normaliser as the last column, the stabiliser."""
+        s = self.spec
+        return [(B, s.heads, s.dim, s.vdim + 1), (B, s.heads)]
+
+    def load(self, get) -> None:
+        """``get(suffix)`` returns the tensor '<layer>.mix.<suffix>'."""
+        self.w_in.zero_()
+        self.w_in[: self.n_in].copy_(torch.cat([get(n).to(self.w_in.dtype) for n in self.cols], dim=0))
+        self.bias_i.copy_(get("i.b").float())
+        self.bias_f.copy_(get("f.b").float())
+        self.norm.copy_(get("norm").float())
+        self.w_o.copy_(get("o"))
+
+    def forward(self, u: torch.Tensor, B: int, T: int, pos_ids: torch.Tensor, states) -> torch.Tensor:
+        s = self.spec
+        c = self.cols
+        memory, stabiliser = states
+        M = B * T
+        proj = F.linear(u, self.w_in)
+        keep = torch.empty((M, s.heads), dtype=torch.float32, device=u.device)
+        take, stab = torch.empty_like(keep), torch.empty_like(keep)
+        N.call("ll_matrix_memory_gates", N.ptr_at(proj, c["i"]), N.ptr_at(proj, c["f"]), N.dtype_code(proj.dtype), proj.stride(0),
+               N.ptr(self.bias_i), N.ptr(self.bias_f), float(s.gate_cap), N.ptr(stabiliser), N.ptr(pos_ids), N.ptr(keep), N.ptr(take),
+               N.ptr(stab), B, T, s.heads, N.stream())
+        y = decay_scan(proj, c["q"], proj, c["k"], proj, c["v"], keep, False, take, None, s.dim ** -0.5, memory, pos_ids, B, T,
+                       s.heads, s.heads, s.dim, s.vdim + 1, unit_col=True)
+        out = gated_group_norm(y, proj, c["g"], self.norm, False, s.eps, s.heads, False, proj.dtype, sigmoid=True, part=s.vdim, stab=stab)
         return F.linear(out, self.w_o)

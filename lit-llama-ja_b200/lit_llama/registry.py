@@ -35,6 +35,10 @@ def _builtin() -> None:
         from .bededra import ARCHITECTURE, Bededra
 
         register_architecture(ARCHITECTURE, Bededra.from_dir)
+    if "Tebodra" not in _FROM_DIR:
+        from .tebodra import ARCHITECTURE, Tebodra
+
+        register_architecture(ARCHITECTURE, Tebodra.from_dir)
 
 
 def load_model_dir(path, dtype: torch.dtype = torch.bfloat16, device="cuda"):
