@@ -310,6 +310,203 @@ static int sa_dispatch(const void* q, int q_stride, const void* gate, int gate_s
   return LL_ERR_UNSUPPORTED;
 }
 
+// ---------------------------------------------------------------------------------------------------------------- attend, tensor-core form
+// Prompts in bf16 (mma.sync m16n8k16, fp32 accumulation).  A block of four warps owns 64 consecutive queries of one head,
+// 16 per warp, whose fragments stay in registers; the keys the tile can see are walked 64 at a time through shared memory
+// (cp.async, rows found by position % ring, dimensions beyond the head's size zero-filled up to D).  S = Q K^T, then scale,
+// cap and mask on the accumulator fragments, an online softmax per row in fp32, and O += P V with the weights split into
+// two bf16 terms p = hi + lo (two products), so that what meets the values carries 16 bits of the fp32 weight and not 8.
+// The sink joins the denominator and the gate multiplies the output in the epilogue.
+constexpr int TM_Q = 64, TM_K = 64, TM_THREADS = 128;
+
+__device__ __forceinline__ void tm_cp_async16(void* smem, const void* gmem) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(smem)), "l"(gmem) : "memory");
+}
+__device__ __forceinline__ void tm_ldmatrix_x4(uint32_t (&r)[4], const void* p) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(smem_u32(p)));
+}
+__device__ __forceinline__ void tm_ldmatrix_x4_trans(uint32_t (&r)[4], const void* p) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(smem_u32(p)));
+}
+// (hi, lo) bf16 pairs of two fp32 numbers: hi = bf16(x), lo = bf16(x - hi)
+__device__ __forceinline__ void tm_split2(float x0, float x1, uint32_t& hi, uint32_t& lo) {
+  const __nv_bfloat16 h0 = __float2bfloat16_rn(x0), h1 = __float2bfloat16_rn(x1);
+  const __nv_bfloat16 l0 = __float2bfloat16_rn(x0 - __bfloat162float(h0)), l1 = __float2bfloat16_rn(x1 - __bfloat162float(h1));
+  hi = (uint32_t)__bfloat16_as_ushort(h0) | ((uint32_t)__bfloat16_as_ushort(h1) << 16);
+  lo = (uint32_t)__bfloat16_as_ushort(l0) | ((uint32_t)__bfloat16_as_ushort(l1) << 16);
+}
+
+template <int D>
+__global__ void __launch_bounds__(TM_THREADS) softmax_attn_mma_kernel(
+    const __nv_bfloat16* __restrict__ q, int q_stride, const __nv_bfloat16* __restrict__ gate, int gate_stride,
+    const __nv_bfloat16* __restrict__ kc, const __nv_bfloat16* __restrict__ vc, const int32_t* __restrict__ pos_ids,
+    const float* __restrict__ sink, float scale, float softcap, int Tn, int H, int G, int dim, int vdim, int window, int chunk, int ring,
+    __nv_bfloat16* __restrict__ y) {
+  constexpr int LD = D + 8, CH = D / 8;
+  __shared__ __align__(16) __nv_bfloat16 Ks[TM_K * LD];
+  __shared__ __align__(16) __nv_bfloat16 Vs[TM_K * LD];
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int t0 = blockIdx.x * TM_Q, h = blockIdx.y, b = blockIdx.z, g = h / (H / G);
+  const int nq = min(TM_Q, Tn - t0);
+  const int p0 = pos_ids[t0];                    // a step's positions are consecutive
+  const uint4 zero4 = make_uint4(0u, 0u, 0u, 0u);
+  for (int c = tid; c < TM_Q * CH; c += TM_THREADS) {
+    const int r = c / CH, ch = c - r * CH;
+    uint4 val = zero4;
+    if (r < nq && ch * 8 < dim) val = *(const uint4*)(q + ((size_t)b * Tn + t0 + r) * q_stride + (size_t)h * dim + ch * 8);
+    *(uint4*)&Ks[r * LD + ch * 8] = val;
+  }
+  __syncthreads();
+  uint32_t qf[D / 16][4];
+#pragma unroll
+  for (int kk = 0; kk < D / 16; ++kk) tm_ldmatrix_x4(qf[kk], &Ks[(warp * 16 + (lane & 15)) * LD + kk * 16 + (lane >> 4) * 8]);
+  __syncthreads();
+  float o[D / 8][4];
+#pragma unroll
+  for (int n = 0; n < D / 8; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
+  float mrow[2] = {-INFINITY, -INFINITY}, lrow[2] = {0.f, 0.f};
+  const int qp[2] = {p0 + warp * 16 + (lane >> 2), p0 + warp * 16 + (lane >> 2) + 8};
+  const int qlo[2] = {sa_first_visible(qp[0], window, chunk), sa_first_visible(qp[1], window, chunk)};
+  const int wlo = sa_first_visible(p0 + warp * 16, window, chunk), whi = p0 + warp * 16 + 15;     // what the warp's rows can see
+  const int khi = p0 + nq - 1;
+  const float inv_cap = softcap > 0.f ? 1.f / softcap : 0.f;
+  const __nv_bfloat16* kbase = kc + ((size_t)b * ring * G + g) * dim;
+  const __nv_bfloat16* vbase = vc + ((size_t)b * ring * G + g) * vdim;
+  for (int kt = sa_first_visible(p0, window, chunk); kt <= khi; kt += TM_K) {
+    for (int c = tid; c < TM_K * CH; c += TM_THREADS) {
+      const int r = c / CH, ch = c - r * CH;
+      const int j = kt + r;
+      const size_t slot = (size_t)(j % ring);
+      if (j <= khi && ch * 8 < dim) tm_cp_async16(&Ks[r * LD + ch * 8], kbase + slot * G * dim + ch * 8);
+      else *(uint4*)&Ks[r * LD + ch * 8] = zero4;
+      if (j <= khi && ch * 8 < vdim) tm_cp_async16(&Vs[r * LD + ch * 8], vbase + slot * G * vdim + ch * 8);
+      else *(uint4*)&Vs[r * LD + ch * 8] = zero4;
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    __syncthreads();
+    if (kt <= whi && kt + TM_K - 1 >= wlo) {       // else: nothing in this tile that a row of this warp sees
+      float sc[TM_K / 8][4];
+#pragma unroll
+      for (int n = 0; n < TM_K / 8; ++n) sc[n][0] = sc[n][1] = sc[n][2] = sc[n][3] = 0.f;
+#pragma unroll
+      for (int kk = 0; kk < D / 16; ++kk) {
+#pragma unroll
+        for (int np = 0; np < TM_K / 16; ++np) {
+          uint32_t bf[4];
+          tm_ldmatrix_x4(bf, &Ks[(np * 16 + (lane & 7) + (lane >> 4) * 8) * LD + kk * 16 + ((lane >> 3) & 1) * 8]);
+          mma_bf16_16816(sc[2 * np], qf[kk][0], qf[kk][1], qf[kk][2], qf[kk][3], bf[0], bf[1]);
+          mma_bf16_16816(sc[2 * np + 1], qf[kk][0], qf[kk][1], qf[kk][2], qf[kk][3], bf[2], bf[3]);
+        }
+      }
+      float tmax[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+      for (int n = 0; n < TM_K / 8; ++n)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int rr = e >> 1;
+          const int kp = kt + n * 8 + (lane & 3) * 2 + (e & 1);
+          float v = sc[n][e] * scale;
+          if (softcap > 0.f) v = softcap * tanhf(v * inv_cap);
+          v = (kp <= qp[rr] && kp >= qlo[rr]) ? v : -INFINITY;
+          sc[n][e] = v;
+          tmax[rr] = fmaxf(tmax[rr], v);
+        }
+      float corr[2], msafe[2];
+#pragma unroll
+      for (int rr = 0; rr < 2; ++rr) {
+        tmax[rr] = fmaxf(tmax[rr], __shfl_xor_sync(0xffffffffu, tmax[rr], 1));
+        tmax[rr] = fmaxf(tmax[rr], __shfl_xor_sync(0xffffffffu, tmax[rr], 2));
+        const float mn = fmaxf(mrow[rr], tmax[rr]);
+        msafe[rr] = mn == -INFINITY ? 0.f : mn;
+        corr[rr] = __expf(mrow[rr] - msafe[rr]);
+        mrow[rr] = mn;
+        lrow[rr] *= corr[rr];
+      }
+#pragma unroll
+      for (int n = 0; n < D / 8; ++n) o[n][0] *= corr[0], o[n][1] *= corr[0], o[n][2] *= corr[1], o[n][3] *= corr[1];
+#pragma unroll
+      for (int n = 0; n < TM_K / 8; ++n)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float pw = __expf(sc[n][e] - msafe[e >> 1]);
+          sc[n][e] = pw;
+          lrow[e >> 1] += pw;
+        }
+#pragma unroll
+      for (int ks = 0; ks < TM_K / 16; ++ks) {
+        uint32_t ah[4], al[4];
+        tm_split2(sc[2 * ks][0], sc[2 * ks][1], ah[0], al[0]);
+        tm_split2(sc[2 * ks][2], sc[2 * ks][3], ah[1], al[1]);
+        tm_split2(sc[2 * ks + 1][0], sc[2 * ks + 1][1], ah[2], al[2]);
+        tm_split2(sc[2 * ks + 1][2], sc[2 * ks + 1][3], ah[3], al[3]);
+#pragma unroll
+        for (int dp = 0; dp < D / 16; ++dp) {
+          uint32_t bf[4];
+          tm_ldmatrix_x4_trans(bf, &Vs[(ks * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * LD + dp * 16 + (lane >> 4) * 8]);
+          mma_bf16_16816(o[2 * dp], ah[0], ah[1], ah[2], ah[3], bf[0], bf[1]);
+          mma_bf16_16816(o[2 * dp + 1], ah[0], ah[1], ah[2], ah[3], bf[2], bf[3]);
+          mma_bf16_16816(o[2 * dp], al[0], al[1], al[2], al[3], bf[0], bf[1]);
+          mma_bf16_16816(o[2 * dp + 1], al[0], al[1], al[2], al[3], bf[2], bf[3]);
+        }
+      }
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int rr = 0; rr < 2; ++rr) {
+    lrow[rr] += __shfl_xor_sync(0xffffffffu, lrow[rr], 1);
+    lrow[rr] += __shfl_xor_sync(0xffffffffu, lrow[rr], 2);
+    const int r = warp * 16 + (lane >> 2) + rr * 8;
+    if (r >= nq) continue;
+    float den = lrow[rr], c1 = 1.f;
+    if (sink) {
+      const float sk = sink[h];
+      const float mn = fmaxf(mrow[rr], sk);
+      c1 = expf(mrow[rr] - mn);
+      den = lrow[rr] * c1 + expf(sk - mn);
+    }
+    const float f = c1 / den;
+    const size_t m = (size_t)b * Tn + t0 + r;
+#pragma unroll
+    for (int n = 0; n < D / 8; ++n) {
+      const int c = n * 8 + (lane & 3) * 2;
+      if (c < vdim) {                            // vdim is a multiple of 8: the pair is inside together
+        float v0 = o[n][rr * 2] * f, v1 = o[n][rr * 2 + 1] * f;
+        if (gate) {
+          const __nv_bfloat162 gg = *(const __nv_bfloat162*)(gate + m * gate_stride + (size_t)h * vdim + c);
+          v0 *= 1.f / (1.f + expf(-__bfloat162float(gg.x)));
+          v1 *= 1.f / (1.f + expf(-__bfloat162float(gg.y)));
+        }
+        *(__nv_bfloat162*)(y + m * H * vdim + (size_t)h * vdim + c) = __floats2bfloat162_rn(v0, v1);
+      }
+    }
+  }
+}
+
+template <int D>
+static int tm_launch(const void* q, int q_stride, const void* gate, int gate_stride, const void* kc, const void* vc, const int32_t* pos_ids,
+                     const float* sink, float scale, float softcap, int B, int Tn, int H, int G, int dim, int vdim, int window, int chunk,
+                     int ring, void* y, cudaStream_t st) {
+  const dim3 grid((Tn + TM_Q - 1) / TM_Q, H, B);
+  softmax_attn_mma_kernel<D><<<grid, TM_THREADS, 0, st>>>((const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)gate, gate_stride,
+                                                          (const __nv_bfloat16*)kc, (const __nv_bfloat16*)vc, pos_ids, sink, scale, softcap,
+                                                          Tn, H, G, dim, vdim, window, chunk, ring, (__nv_bfloat16*)y);
+  LL_LAUNCH_OK("softmax_attn_mma_kernel");
+  return LL_OK;
+}
+
+// The tensor-core form takes bf16 heads of up to 128 dimensions in multiples of 8 (16-byte rows), gates and queries on
+// 4-byte / 16-byte boundaries.
+static bool tm_supported(int dtype, int T, int dim, int vdim, int q_stride, int gate_stride, int splits) {
+  return dtype == LL_BF16 && splits == 1 && T >= 16 && dim % 8 == 0 && vdim % 8 == 0 && dim <= 128 && vdim <= 128 && q_stride % 8 == 0 &&
+         gate_stride % 2 == 0;
+}
+
 }  // namespace llb
 
 using namespace llb;
@@ -360,7 +557,15 @@ int ll_softmax_attn(const void* q, int q_stride, const void* gate, int gate_stri
   }
   if (B == 0 || T == 0) return LL_OK;
   cudaStream_t st = (cudaStream_t)stream;
-  (void)form;
+  if (form == 0 && tm_supported(dtype, T, dim, vdim, q_stride, gate ? gate_stride : 0, splits)) {
+    const int d = dim > vdim ? dim : vdim;
+#define LL_TM(DD)                                                                                                                   \
+  if (d <= DD)                                                                                                                      \
+    return tm_launch<DD>(q, q_stride, gate, gate_stride, kc, vc, pos_ids, sink, scale, softcap, B, T, H, G, dim, vdim, window, chunk, ring, \
+                         y, st);
+    LL_TM(32) LL_TM(64) LL_TM(96) LL_TM(128)
+#undef LL_TM
+  }
   if (dtype == LL_F32)
     return sa_dispatch<float>(q, q_stride, gate, gate_stride, kc, vc, pos_ids, sink, scale, softcap, B, T, H, G, dim, vdim, window, chunk,
                               ring, splits, scratch, y, st);

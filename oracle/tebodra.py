@@ -148,12 +148,15 @@ def mlstm(h, W, p, m, eps):
         o_t = S_t^T q_t / (max(|n_t . q_t|, e^(-mx_t)) + 1e-6)
     then every head divided by its root mean square, a weight over all heads, a sigmoid gate, the output projection."""
     T = h.shape[0]
-    H, d, e, cap = m["heads"], m["dim"], m["vdim"], float(m["gate_cap"])
+    H, d, e, cap = m["heads"], m["dim"], m["vdim"], float(m.get("gate_cap") or 0.0)
+
+    def capped(z):                      # a cap of 0 (or none) leaves the pre-activation as it is
+        return cap * np.tanh(z / cap) if cap > 0 else z
     q = (h @ W[p + "q"].T).reshape(T, H, d) * d ** -0.5
     k = (h @ W[p + "k"].T).reshape(T, H, d)
     v = (h @ W[p + "v"].T).reshape(T, H, e)
-    gi = cap * np.tanh((h @ W[p + "i"].T + W[p + "i.b"]) / cap)
-    gf = log_sigmoid(cap * np.tanh((h @ W[p + "f"].T + W[p + "f.b"]) / cap))
+    gi = capped(h @ W[p + "i"].T + W[p + "i.b"])
+    gf = log_sigmoid(capped(h @ W[p + "f"].T + W[p + "f.b"]))
     out = np.zeros((T, H, e))
     for a in range(H):
         S, n, mx = np.zeros((d, e)), np.zeros(d), 0.0
