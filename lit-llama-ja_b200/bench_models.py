@@ -1,6 +1,6 @@
 """Throughput of a model family beside its closest relative at equal size: prefill tokens/s, batch-1 decode tokens/s, and
 the hot kernels of each timed alone against the measured roofline.  ``bench.py --family lepalorn``: Lepalorn beside LLaMA;
-``bench.py --family bededra``: Bededra beside Lepalorn.  Random weights, layer shapes of real
+``bench.py --family bededra``: Bededra beside Lepalorn; ``bench.py --family tebodra``: Tebodra beside Bededra.  Random weights, layer shapes of real
 models, a few layers each (every layer costs the same).  Timing: CUDA events, warm-up, an L2 flush (a 256 MB write)
 between timed iterations."""
 from __future__ import annotations
@@ -368,11 +368,183 @@ def run_bededra(args):
     return 0
 
 
+# Tebodra at the widths of SIZES, as deep as Bededra there.  Layers cycle through: attention_2 with a chunk mask (the size of
+# Bededra's window), matrix memory, attention over the whole past (filters of 4 taps, half of every head rotated), attention_2
+# reading the first layer's ring.  Attention heads as Bededra's; the matrix memory's values span the width, its keys half of
+# that; a dense feed-forward of 4 x width.
+TEBODRA_SIZES = {
+    "w1024": dict(width=1024, layers=4, heads=8, kv=2, dim=64, chunk=512, m_heads=4, m_dim=128, m_vdim=256, ff=4096),
+    "w2048": dict(width=2048, layers=4, heads=16, kv=4, dim=128, chunk=1024, m_heads=8, m_dim=128, m_vdim=256, ff=8192),
+    "w4096": dict(width=4096, layers=2, heads=32, kv=8, dim=128, chunk=2048, m_heads=16, m_dim=128, m_vdim=256, ff=16384),
+}
+
+
+def tebodra_model(s, device, dtype=torch.bfloat16):
+    from lit_llama.tebodra import Tebodra, TebodraConfig
+
+    ff = {"kind": "dense", "ff": s["ff"]}
+    D = s["dim"]
+    chunked = {"type": "attention_2", "mlp": ff, "mixer": {
+        "heads": s["heads"], "kv_heads": s["kv"], "dim": D, "vdim": D, "scale": D ** -0.5, "mask": {"size": s["chunk"]},
+        "rot": {"base": 10000.0, "dims": D, "scaling": {"factor": 4.0}}}}
+    memory = {"type": "mlstm", "mlp": None, "mixer": {"heads": s["m_heads"], "dim": s["m_dim"], "vdim": s["m_vdim"], "gate_cap": 15.0}}
+    full = {"type": "attention", "mlp": ff, "mixer": {
+        "heads": s["heads"], "kv_heads": s["kv"], "dim": D, "vdim": D, "scale": D ** -0.5, "conv": 4, "softcap": 50.0,
+        "rot": {"base": 500000.0, "dims": D // 2, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}}}
+    borrow = {"type": "attention_2", "mlp": ff, "mixer": dict(chunked["mixer"], kv_from=0)}
+    cycle = [chunked, memory, full, borrow] if s["layers"] >= 4 else [full, memory]
+    cfg = {"vocab": VOCAB, "width": s["width"], "norm": {"eps": 1e-5}, "residual_mult": 0.5,
+           "layers": [cycle[i % len(cycle)] for i in range(s["layers"])]}
+    m = Tebodra(TebodraConfig.from_dict(cfg), dtype=dtype, device=device)
+    g = torch.Generator(device=device).manual_seed(0)
+    for n, p in m.named_parameters():
+        leaf = n.rsplit(".", 1)[-1]
+        if p.dim() >= 2 and "conv" not in n:
+            p.copy_((torch.randn(p.shape, generator=g, device=device) / math.sqrt(p.shape[-1])).to(p.dtype))
+        elif p.dim() >= 2:
+            p.copy_(0.3 * torch.randn(p.shape, generator=g, device=device))
+        elif leaf == "bias_f":
+            p.fill_(3.0)
+    return m.eval()
+
+
+def tebodra_kernel_table(s, model, device, timer, prompt_len):
+    """The mixers' kernels alone, one layer of each kind.  Roofline time = max(flops / tensor peak, bytes / copy bandwidth),
+    flops and bytes counted for the mechanism (one sweep over the visible keys; one update and one read-out of the memory
+    per token), not for what the kernel happens to do."""
+    from torch.nn import functional as F
+
+    from lit_llama.bededra import add_norm_pair
+    from lit_llama.recurrence import decay_scan, gated_group_norm
+
+    hbm, tflops, which = peaks()
+    bf = torch.bfloat16
+    rows = []
+
+    def add(name, t, flops, nbytes):
+        roof = max(flops / tflops, nbytes / hbm)
+        rows.append(dict(kernel=name, us=round(t * 1e6, 1), roofline_us=round(roof * 1e6, 2), fraction=round(roof / t, 4)))
+
+    E, H, G, D = s["width"], s["heads"], s["kv"], s["dim"]
+    blocks = {}
+    for i, b in enumerate(model.blocks):
+        key = b.kind if b.kind == "mlstm" or b.mix.owner else "borrow"
+        blocks.setdefault(key, (i, b))
+    for T, tag in ((prompt_len, "prefill"), (1, "decode")):
+        pos0 = 0 if T > 1 else prompt_len
+        pos_ids = torch.arange(pos0, pos0 + T, dtype=torch.int32, device=device)
+        model.reset_cache()
+        model._begin(1, prompt_len + 64, True)
+        for t in model.kv_caches:
+            t.normal_()
+        for t in model.states:
+            t.zero_()
+        x = torch.randn((T, E), device=device, dtype=bf)
+        sms = torch.cuda.get_device_properties(device).multi_processor_count
+        for kind, label in (("attention", "whole past, filters, cap"), ("attention_2", "chunk, norms, sink")):
+            if kind not in blocks:
+                continue
+            i, blk = blocks[kind]
+            att, spec = blk.mix, blk.mix.spec
+            n = model._cache_of[i]
+            caches = model.kv_caches[2 * n:2 * n + 2]
+            proj = F.linear(x, att.w_in)
+            conv_state = torch.zeros(att.conv.state_shape(1), device=device) if att.conv is not None else None
+            reach = spec.reach or (1 << 30)
+            span = min(reach, caches[0].shape[1])
+            splits = 1 if T > 1 else max(1, min(64, (2 * sms) // max(1, (H + 3) // 4), (span + 127) // 128))
+            keys = sum(p - (0 if spec.chunk is None else (p // spec.chunk) * spec.chunk) + 1 for p in range(pos0, pos0 + T))
+            rows_read = min(pos0 + T, (reach if T == 1 else pos0 + T))
+
+            def attn():
+                att.attend(proj, 1, T, pos_ids, caches, conv_state, splits)
+
+            add(f"rotary_attn {tag} ({label}: filter + norm/rotation/append + attention + gate)", timer(attn, graph=True),
+                2.0 * keys * H * 2 * D, 2.0 * (rows_read * G * 2 * D + 3 * T * H * D))
+        # matrix memory: gates, the walk with its normaliser column, the read-out norm
+        _, mem = blocks["mlstm"]
+        mm, ms = mem.mix, mem.mix.spec
+        proj = F.linear(x, mm.w_in)
+        c = mm.cols
+        keep = torch.rand((T, ms.heads), device=device) * 0.1 + 0.9
+        take = torch.rand((T, ms.heads), device=device)
+        stab = torch.zeros((T, ms.heads), device=device)
+        memory = torch.zeros((1, ms.heads, ms.dim, ms.vdim + 1), device=device)
+        mstate = torch.zeros((1, ms.heads), device=device)
+        from lit_llama import _native as N
+
+        def gates():
+            N.call("ll_matrix_memory_gates", N.ptr_at(proj, c["i"]), N.ptr_at(proj, c["f"]), N.dtype_code(bf), proj.stride(0),
+                   N.ptr(mm.bias_i), N.ptr(mm.bias_f), float(ms.gate_cap), N.ptr(mstate), N.ptr(pos_ids), N.ptr(keep), N.ptr(take),
+                   N.ptr(stab), 1, T, ms.heads, N.stream())
+
+        add(f"matrix_memory_gates {tag}", timer(gates, graph=True), 0.0, T * ms.heads * (4 + 12))
+        keep.uniform_(0.9, 1.0)
+        take.uniform_(0.0, 1.0)
+
+        def walk():
+            decay_scan(proj, c["q"], proj, c["k"], proj, c["v"], keep, False, take, None, ms.dim ** -0.5, memory, pos_ids, 1, T, ms.heads,
+                       ms.heads, ms.dim, ms.vdim + 1, unit_col=True)
+
+        nst = ms.heads * ms.dim * (ms.vdim + 1)
+        add(f"decay_scan {tag} (matrix memory + normaliser)", timer(walk, graph=True), 4.0 * T * nst,
+            2.0 * T * ms.heads * (2 * ms.dim + ms.vdim) + 4.0 * T * ms.heads * (2 + ms.vdim + 1) + 8.0 * nst)
+        yv = torch.randn((T, ms.heads * (ms.vdim + 1)), device=device)
+        add(f"read-out norm + gate {tag}", timer(lambda: gated_group_norm(yv, proj, c["g"], mm.norm, False, 1e-5, ms.heads, False, bf,
+                                                                          sigmoid=True, part=ms.vdim, stab=stab), graph=True),
+            0.0, T * ms.heads * ms.vdim * (4 + 2 + 2))
+        xs = torch.randn((T, E), device=device)
+        h1 = torch.empty((T, E), device=device, dtype=bf)
+        a0 = torch.randn((T, E), device=device, dtype=bf)
+        add(f"add + norm {tag}", timer(lambda: add_norm_pair(xs, [(a0, 0.5)], mem.norm1, None, 1e-5, h1, None, bf), graph=True), 0.0,
+            T * E * (4 + 4 + 2 + 4 + 2))
+        hh = torch.randn((T, s["ff"]), device=device, dtype=bf)
+        add(f"gelu {tag}", timer(lambda: N.call("ll_gelu", N.ptr(hh), N.dtype_code(bf), 0, hh.numel(), N.stream()), graph=True), 0.0,
+            T * s["ff"] * 4)
+    return rows, which
+
+
+def run_tebodra(args):
+    import sys
+
+    sys.path.insert(0, str(ROOT))
+    from __graft_entry__ import build
+
+    build()
+    device = torch.device("cuda", 0)
+    torch.cuda.set_device(device)
+    timer = Timer(device)
+    prompt_len = 2048
+    out = {"family": "tebodra", "beside": "bededra", "dtype": "bf16", "data": "synthetic (random weights)", "prompt_len": prompt_len,
+           "batch": 1, "l2": "256 MB written between timed iterations", "sizes": {}}
+    names = [n for n in TEBODRA_SIZES if not getattr(args, "size", None) or n == args.size]
+    for name in names:
+        s = TEBODRA_SIZES[name]
+        with torch.no_grad():
+            m = tebodra_model(s, device)
+            pre, dec = end_to_end(m, timer, prompt_len, device, prompt_len + 64)
+            rows, which = tebodra_kernel_table(s, m, device, timer, prompt_len)
+            del m
+            torch.cuda.empty_cache()
+            bed = bededra_model(BEDEDRA_SIZES[name], device)
+            bpre, bdec = end_to_end(bed, timer, prompt_len, device, prompt_len + 64)
+            brows, _ = bededra_kernel_table(BEDEDRA_SIZES[name], bed, device, timer, prompt_len)
+            del bed
+            torch.cuda.empty_cache()
+        out["sizes"][name] = {"config": s, "tebodra": {"prefill_tokens_per_s": round(pre), "decode_tokens_per_s": round(dec, 1)},
+                              "bededra_same_width": {"prefill_tokens_per_s": round(bpre), "decode_tokens_per_s": round(bdec, 1)},
+                              "kernels": rows, "bededra_kernels": brows, "roofline": f"of {which}"}
+    print(json.dumps(out))
+    return 0
+
+
 def run(args):
     import sys
 
     if args.family == "bededra":
         return run_bededra(args)
+    if args.family == "tebodra":
+        return run_tebodra(args)
     sys.path.insert(0, str(ROOT))
     from __graft_entry__ import build
 

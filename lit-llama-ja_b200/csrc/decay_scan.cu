@@ -181,8 +181,11 @@ __global__ void channel_decay_kernel(const T* __restrict__ z, int stride, const 
 // of the input projection's output, li = cap(raw_i + bi), lf = logsigmoid(cap(raw_f + bf)), cap(z) = c tanh(z / c) (c <= 0:
 // no cap), and mx carried from token to token (0 at a sequence's start, not minus infinity):
 //   mx_t = max(lf_t + mx_(t-1), li_t);   keep_t = exp(lf_t + mx_(t-1) - mx_t);   take_t = exp(li_t - mx_t)
-// A warp owns one (sequence, head): 32 tokens are loaded and turned into (li, lf) in parallel, the walk over them runs in
-// registers of every lane alike (two shuffles a token), lane t keeps token t's results.
+// A warp owns one (sequence, head) and takes 32 tokens a round, one per lane.  Token t acts on the stabiliser as the map
+// mx -> max(mx + lf_t, li_t); two such maps compose to one of the same form, (F, M) then (F', M') = (F + F', max(M + F', M')),
+// so the 32 maps of a round are composed by a shuffle scan (five steps) and applied to the round's incoming mx.  Every
+// token's keep uses as mx_(t-1) exactly the value its left neighbour reports as mx_t: the recurrence the walk then runs is
+// consistent, and what it computes does not depend on the stabiliser's rounding.
 template <typename T>
 __global__ void matrix_memory_gates_kernel(const T* __restrict__ raw_i, const T* __restrict__ raw_f, int stride,
                                            const float* __restrict__ bias_i, const float* __restrict__ bias_f, float cap,
@@ -195,30 +198,40 @@ __global__ void matrix_memory_gates_kernel(const T* __restrict__ raw_i, const T*
   float mx = pos_ids[0] == 0 ? 0.f : mstate[w];
   const float bi = bias_i ? bias_i[h] : 0.f, bf = bias_f ? bias_f[h] : 0.f;
   const float inv = cap > 0.f ? 1.f / cap : 0.f;
+  auto fetch = [&](int t, float& zi, float& zf) {
+    const bool ok = t < Tn;
+    const size_t m = (size_t)b * Tn + (ok ? t : 0);
+    zi = ok ? dt<T>::ld(raw_i, m * stride + h) : 0.f;
+    zf = ok ? dt<T>::ld(raw_f, m * stride + h) : 0.f;
+  };
+  float ni, nf;
+  fetch(lane, ni, nf);
   for (int t0 = 0; t0 < Tn; t0 += 32) {
     const int t = t0 + lane;
-    float li = 0.f, lf = 0.f;
-    if (t < Tn) {
-      const size_t m = (size_t)b * Tn + t;
-      float zi = dt<T>::ld(raw_i, m * stride + h) + bi, zf = dt<T>::ld(raw_f, m * stride + h) + bf;
-      if (cap > 0.f) zi = cap * tanhf(zi * inv), zf = cap * tanhf(zf * inv);
-      li = zi;
-      lf = fminf(zf, 0.f) - log1pf(expf(-fabsf(zf)));          // log sigmoid
+    float zi = ni + bi, zf = nf + bf;
+    if (t0 + 32 < Tn) fetch(t + 32, ni, nf);                  // the next round's loads fly under this round's scan
+    if (cap > 0.f) zi = cap * tanhf(zi * inv), zf = cap * tanhf(zf * inv);
+    const float li = t < Tn ? zi : -INFINITY;                 // tokens past the end are the identity map (F = 0, M = -inf)
+    const float lf = t < Tn ? fminf(zf, 0.f) - log1pf(expf(-fabsf(zf))) : 0.f;       // log sigmoid
+    float F = lf, M = li;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+      const float pF = __shfl_up_sync(0xffffffffu, F, d), pM = __shfl_up_sync(0xffffffffu, M, d);
+      if (lane >= d) {
+        M = fmaxf(pM + F, M);
+        F = pF + F;
+      }
     }
-    const int nt = min(32, Tn - t0);
-    float my_prev = 0.f, my_new = 0.f;
-    for (int tt = 0; tt < nt; ++tt) {
-      const float f = __shfl_sync(0xffffffffu, lf, tt), i = __shfl_sync(0xffffffffu, li, tt);
-      const float mn = fmaxf(f + mx, i);
-      if (lane == tt) my_prev = mx, my_new = mn;
-      mx = mn;
-    }
+    const float my_new = fmaxf(mx + F, M);
+    float my_prev = __shfl_up_sync(0xffffffffu, my_new, 1);
+    if (lane == 0) my_prev = mx;
     if (t < Tn) {
       const size_t o = ((size_t)b * Tn + t) * H + h;
       keep[o] = expf(lf + my_prev - my_new);
       take[o] = expf(li - my_new);
       stab[o] = my_new;
     }
+    mx = __shfl_sync(0xffffffffu, my_new, 31);
   }
   if (lane == 0) mstate[w] = mx;
 }

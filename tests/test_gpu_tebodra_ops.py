@@ -205,7 +205,7 @@ def _gates(zi, zf, cap):
         new = np.maximum(lf[t] + mx, li[t])
         keep[t], take[t], stab[t] = np.exp(lf[t] + mx - new), np.exp(li[t] - new), new
         mx = new
-    return keep, take, stab
+    return keep, take, stab, li, lf
 
 
 @pytest.mark.parametrize("cap", [0.0, 4.0])
@@ -229,9 +229,13 @@ def test_exponential_gates_and_their_stabiliser(cap, portions):
                N.ptr(pd), N.ptr(k), N.ptr(t), N.ptr(s), 1, n, H, N.stream())
         outs.append([host(k), host(t), host(s)])
         at += n
-    for j in range(3):
-        got = np.concatenate([o[j] for o in outs])
-        assert np.abs(got - want[j]).max() < 1e-5 * max(1.0, np.abs(want[j]).max())
+    keep, take, stab = (np.concatenate([o[j] for o in outs]) for j in range(3))
+    # the stabiliser may be rounded in another order than the token-by-token walk (its sums run over up to 32 tokens) ...
+    assert np.abs(stab - want[2]).max() < 2e-4 and np.abs(keep - want[0]).max() < 2e-4 and np.abs(take / want[1] - 1).max() < 2e-4
+    # ... but the gates must be exactly those of the stabiliser that is reported: the memory then does not depend on it
+    li, lf = want[3], want[4]
+    prev = np.concatenate([np.zeros((1, H)), stab[:-1]])
+    assert np.abs(keep - np.exp(lf + prev - stab)).max() < 2e-6 and np.abs(take / np.exp(li - stab) - 1).max() < 1e-5
 
 
 @pytest.mark.parametrize("n,p", [(1, 1), (7, 5), (16, 64), (48, 65), (130, 3)])
