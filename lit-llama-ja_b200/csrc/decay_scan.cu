@@ -181,19 +181,24 @@ __global__ void channel_decay_kernel(const T* __restrict__ z, int stride, const 
 // of the input projection's output, li = cap(raw_i + bi), lf = logsigmoid(cap(raw_f + bf)), cap(z) = c tanh(z / c) (c <= 0:
 // no cap), and mx carried from token to token (0 at a sequence's start, not minus infinity):
 //   mx_t = max(lf_t + mx_(t-1), li_t);   keep_t = exp(lf_t + mx_(t-1) - mx_t);   take_t = exp(li_t - mx_t)
-// A warp owns one (sequence, head) and takes 32 tokens a round, one per lane.  Token t acts on the stabiliser as the map
-// mx -> max(mx + lf_t, li_t); two such maps compose to one of the same form, (F, M) then (F', M') = (F + F', max(M + F', M')),
-// so the 32 maps of a round are composed by a shuffle scan (five steps) and applied to the round's incoming mx.  Every
-// token's keep uses as mx_(t-1) exactly the value its left neighbour reports as mx_t: the recurrence the walk then runs is
-// consistent, and what it computes does not depend on the stabiliser's rounding.
+// A block owns one (sequence, head) and takes MG_THREADS tokens a round, one per thread.  Token t acts on the stabiliser as
+// the map mx -> max(mx + lf_t, li_t); two such maps compose to one of the same form, (F, M) then (F', M') = (F + F',
+// max(M + F', M')), so a warp composes its 32 maps by a shuffle scan (five steps), the warps' totals meet in shared memory,
+// and every thread applies what lies before it to the round's incoming mx.  Every token's keep uses as mx_(t-1) exactly the
+// value its left neighbour reports as mx_t: the recurrence the walk then runs is consistent, and what it computes does not
+// depend on the stabiliser's rounding.  The transcendental part (cap, log sigmoid, exponentials) of a round's tokens runs
+// in parallel; only the few compositions per round are sequential.
+constexpr int MG_THREADS = 256;
+
 template <typename T>
-__global__ void matrix_memory_gates_kernel(const T* __restrict__ raw_i, const T* __restrict__ raw_f, int stride,
-                                           const float* __restrict__ bias_i, const float* __restrict__ bias_f, float cap,
-                                           float* __restrict__ mstate, const int32_t* __restrict__ pos_ids, float* __restrict__ keep,
-                                           float* __restrict__ take, float* __restrict__ stab, int Tn, int H, int BH) {
-  const int w = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  if (w >= BH) return;
-  const int lane = threadIdx.x & 31;
+__global__ void __launch_bounds__(MG_THREADS) matrix_memory_gates_kernel(
+    const T* __restrict__ raw_i, const T* __restrict__ raw_f, int stride, const float* __restrict__ bias_i,
+    const float* __restrict__ bias_f, float cap, float* __restrict__ mstate, const int32_t* __restrict__ pos_ids,
+    float* __restrict__ keep, float* __restrict__ take, float* __restrict__ stab, int Tn, int H) {
+  constexpr int NW = MG_THREADS / 32;
+  __shared__ float wF[2][NW], wM[2][NW];
+  const int w = blockIdx.x;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int b = w / H, h = w - b * H;
   float mx = pos_ids[0] == 0 ? 0.f : mstate[w];
   const float bi = bias_i ? bias_i[h] : 0.f, bf = bias_f ? bias_f[h] : 0.f;
@@ -205,13 +210,14 @@ __global__ void matrix_memory_gates_kernel(const T* __restrict__ raw_i, const T*
     zf = ok ? dt<T>::ld(raw_f, m * stride + h) : 0.f;
   };
   float ni, nf;
-  fetch(lane, ni, nf);
-  for (int t0 = 0; t0 < Tn; t0 += 32) {
-    const int t = t0 + lane;
+  fetch(threadIdx.x, ni, nf);
+  int buf = 0;
+  for (int t0 = 0; t0 < Tn; t0 += MG_THREADS, buf ^= 1) {
+    const int t = t0 + threadIdx.x;
     float zi = ni + bi, zf = nf + bf;
-    if (t0 + 32 < Tn) fetch(t + 32, ni, nf);                  // the next round's loads fly under this round's scan
+    if (t0 + MG_THREADS < Tn) fetch(t + MG_THREADS, ni, nf);   // the next round's loads fly under this round's scan
     if (cap > 0.f) zi = cap * tanhf(zi * inv), zf = cap * tanhf(zf * inv);
-    const float li = t < Tn ? zi : -INFINITY;                 // tokens past the end are the identity map (F = 0, M = -inf)
+    const float li = t < Tn ? zi : -INFINITY;                  // tokens past the end are the identity map (F = 0, M = -inf)
     const float lf = t < Tn ? fminf(zf, 0.f) - log1pf(expf(-fabsf(zf))) : 0.f;       // log sigmoid
     float F = lf, M = li;
 #pragma unroll
@@ -222,18 +228,26 @@ __global__ void matrix_memory_gates_kernel(const T* __restrict__ raw_i, const T*
         F = pF + F;
       }
     }
-    const float my_new = fmaxf(mx + F, M);
+    if (lane == 31) wF[buf][warp] = F, wM[buf][warp] = M;
+    __syncthreads();                                           // (the other buffer is free again: its readers passed this barrier a round ago)
+    float m_in = mx, m_out = mx;
+#pragma unroll
+    for (int ww = 0; ww < NW; ++ww) {
+      m_out = fmaxf(m_out + wF[buf][ww], wM[buf][ww]);
+      if (ww + 1 == warp) m_in = m_out;
+    }
+    const float my_new = fmaxf(m_in + F, M);
     float my_prev = __shfl_up_sync(0xffffffffu, my_new, 1);
-    if (lane == 0) my_prev = mx;
+    if (lane == 0) my_prev = m_in;
     if (t < Tn) {
       const size_t o = ((size_t)b * Tn + t) * H + h;
       keep[o] = expf(lf + my_prev - my_new);
       take[o] = expf(li - my_new);
       stab[o] = my_new;
     }
-    mx = __shfl_sync(0xffffffffu, my_new, 31);
+    mx = m_out;
   }
-  if (lane == 0) mstate[w] = mx;
+  if (threadIdx.x == 0) mstate[w] = mx;
 }
 
 }  // namespace llb
@@ -328,14 +342,14 @@ int ll_matrix_memory_gates(const void* raw_i, const void* raw_f, int dtype, int 
                "bad matrix_memory_gates arguments");
   if (B == 0 || T == 0) return LL_OK;
   cudaStream_t st = (cudaStream_t)stream;
-  const int BH = B * H;
-  const unsigned blocks = (unsigned)((BH + 3) / 4);
+  const unsigned blocks = (unsigned)(B * H);
   if (dtype == LL_F32)
-    matrix_memory_gates_kernel<float><<<blocks, 128, 0, st>>>((const float*)raw_i, (const float*)raw_f, stride, bias_i, bias_f, cap, mstate,
-                                                             pos_ids, keep, take, stab, T, H, BH);
+    matrix_memory_gates_kernel<float><<<blocks, MG_THREADS, 0, st>>>((const float*)raw_i, (const float*)raw_f, stride, bias_i, bias_f, cap,
+                                                                    mstate, pos_ids, keep, take, stab, T, H);
   else if (dtype == LL_BF16)
-    matrix_memory_gates_kernel<__nv_bfloat16><<<blocks, 128, 0, st>>>((const __nv_bfloat16*)raw_i, (const __nv_bfloat16*)raw_f, stride,
-                                                                     bias_i, bias_f, cap, mstate, pos_ids, keep, take, stab, T, H, BH);
+    matrix_memory_gates_kernel<__nv_bfloat16><<<blocks, MG_THREADS, 0, st>>>((const __nv_bfloat16*)raw_i, (const __nv_bfloat16*)raw_f,
+                                                                            stride, bias_i, bias_f, cap, mstate, pos_ids, keep, take,
+                                                                            stab, T, H);
   else {
     set_error("matrix_memory_gates: unsupported dtype %d", dtype);
     return LL_ERR_UNSUPPORTED;
