@@ -323,7 +323,7 @@ def bededra_kernel_table(s, model, device, timer, prompt_len):
         # the layer's short convolution and its two norms (bandwidth)
         xs = torch.randn((T, E), device=device)
         h1, h2 = torch.empty((T, E), device=device), torch.empty((T, E), device=device, dtype=bf)
-        from lit_llama.bededra import add_norm_pair
+        from lit_llama.stepping import add_norm_pair
 
         a0 = torch.randn((T, E), device=device, dtype=bf)
         add(f"add + two norms {tag}", timer(lambda: add_norm_pair(xs, [(a0, 1.0), (a0, 0.5)], par.norm1, par.norm2, 1e-5, h1, h2, bf),
@@ -414,7 +414,7 @@ def tebodra_kernel_table(s, model, device, timer, prompt_len):
     per token), not for what the kernel happens to do."""
     from torch.nn import functional as F
 
-    from lit_llama.bededra import add_norm_pair
+    from lit_llama.stepping import add_norm_pair
     from lit_llama.recurrence import decay_scan, gated_group_norm
 
     hbm, tflops, which = peaks()

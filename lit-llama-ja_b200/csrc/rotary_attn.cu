@@ -313,7 +313,8 @@ static int sa_dispatch(const void* q, int q_stride, const void* gate, int gate_s
 // ---------------------------------------------------------------------------------------------------------------- attend, tensor-core form
 // Prompts in bf16 (mma.sync m16n8k16, fp32 accumulation).  A block of four warps owns 64 consecutive queries of one head,
 // 16 per warp, whose fragments stay in registers; the keys the tile can see are walked 64 at a time through shared memory
-// (cp.async, rows found by position % ring, dimensions beyond the head's size zero-filled up to D).  S = Q K^T, then scale,
+// (cp.async into two stages, the next tile under the current one's math; rows found by position % ring, dimensions beyond
+// the head's size zero-filled up to D).  S = Q K^T, then scale,
 // cap and mask on the accumulator fragments, an online softmax per row in fp32, and O += P V with the weights split into
 // two bf16 terms p = hi + lo (two products), so that what meets the values carries 16 bits of the fp32 weight and not 8.
 // The sink joins the denominator and the gate multiplies the output in the epilogue.
@@ -340,17 +341,23 @@ __device__ __forceinline__ void tm_split2(float x0, float x1, uint32_t& hi, uint
   lo = (uint32_t)__bfloat16_as_ushort(l0) | ((uint32_t)__bfloat16_as_ushort(l1) << 16);
 }
 
+// tanh from one fast exponential and one fast division (relative error about 1e-6 of the result for arguments of order one,
+// 1e-4 for arguments of 1e-3: far below the 2^-9 of the bf16 operands this form works on)
+__device__ __forceinline__ float tm_tanh(float x) { return 1.f - __fdividef(2.f, 1.f + __expf(2.f * x)); }
+
 template <int D>
-__global__ void __launch_bounds__(TM_THREADS) softmax_attn_mma_kernel(
+__global__ void __launch_bounds__(TM_THREADS, 3) softmax_attn_mma_kernel(
     const __nv_bfloat16* __restrict__ q, int q_stride, const __nv_bfloat16* __restrict__ gate, int gate_stride,
     const __nv_bfloat16* __restrict__ kc, const __nv_bfloat16* __restrict__ vc, const int32_t* __restrict__ pos_ids,
     const float* __restrict__ sink, float scale, float softcap, int Tn, int H, int G, int dim, int vdim, int window, int chunk, int ring,
     __nv_bfloat16* __restrict__ y) {
-  constexpr int LD = D + 8, CH = D / 8;
-  __shared__ __align__(16) __nv_bfloat16 Ks[TM_K * LD];
-  __shared__ __align__(16) __nv_bfloat16 Vs[TM_K * LD];
+  constexpr int LD = D + 8, CH = D / 8, STAGE = 2 * TM_K * LD;      // a stage: 64 key rows, then 64 value rows
+  extern __shared__ __align__(16) unsigned char tm_smem[];
+  __nv_bfloat16* const stages = (__nv_bfloat16*)tm_smem;
+  __nv_bfloat16* Ks = stages;                                       // (the queries pass through stage 0 first)
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int t0 = blockIdx.x * TM_Q, h = blockIdx.y, b = blockIdx.z, g = h / (H / G);
+  // late query tiles walk the most keys: they are launched first, so that the long blocks do not end up as the tail
+  const int t0 = ((int)gridDim.x - 1 - (int)blockIdx.x) * TM_Q, h = blockIdx.y, b = blockIdx.z, g = h / (H / G);
   const int nq = min(TM_Q, Tn - t0);
   const int p0 = pos_ids[t0];                    // a step's positions are consecutive
   const uint4 zero4 = make_uint4(0u, 0u, 0u, 0u);
@@ -376,19 +383,37 @@ __global__ void __launch_bounds__(TM_THREADS) softmax_attn_mma_kernel(
   const float inv_cap = softcap > 0.f ? 1.f / softcap : 0.f;
   const __nv_bfloat16* kbase = kc + ((size_t)b * ring * G + g) * dim;
   const __nv_bfloat16* vbase = vc + ((size_t)b * ring * G + g) * vdim;
-  for (int kt = sa_first_visible(p0, window, chunk); kt <= khi; kt += TM_K) {
+  // the next tile's rows are copied under the current tile's math: two stages, one cp.async group per tile
+  auto load_tile = [&](int kt, int st) {
+    __nv_bfloat16* Kd = stages + st * STAGE;
+    __nv_bfloat16* Vd = Kd + TM_K * LD;
     for (int c = tid; c < TM_K * CH; c += TM_THREADS) {
       const int r = c / CH, ch = c - r * CH;
       const int j = kt + r;
       const size_t slot = (size_t)(j % ring);
-      if (j <= khi && ch * 8 < dim) tm_cp_async16(&Ks[r * LD + ch * 8], kbase + slot * G * dim + ch * 8);
-      else *(uint4*)&Ks[r * LD + ch * 8] = zero4;
-      if (j <= khi && ch * 8 < vdim) tm_cp_async16(&Vs[r * LD + ch * 8], vbase + slot * G * vdim + ch * 8);
-      else *(uint4*)&Vs[r * LD + ch * 8] = zero4;
+      if (j <= khi && ch * 8 < dim) tm_cp_async16(&Kd[r * LD + ch * 8], kbase + slot * G * dim + ch * 8);
+      else *(uint4*)&Kd[r * LD + ch * 8] = zero4;
+      if (j <= khi && ch * 8 < vdim) tm_cp_async16(&Vd[r * LD + ch * 8], vbase + slot * G * vdim + ch * 8);
+      else *(uint4*)&Vd[r * LD + ch * 8] = zero4;
     }
     asm volatile("cp.async.commit_group;" ::: "memory");
-    asm volatile("cp.async.wait_group 0;" ::: "memory");
+  };
+  const int wlo_last = sa_first_visible(whi, window, chunk);
+  const int kt0 = sa_first_visible(p0, window, chunk);
+  load_tile(kt0, 0);
+  int st = 0;
+  for (int kt = kt0; kt <= khi; kt += TM_K, st ^= 1) {
+    if (kt + TM_K <= khi) {
+      load_tile(kt + TM_K, st ^ 1);
+      asm volatile("cp.async.wait_group 1;" ::: "memory");
+    } else {
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
+    }
     __syncthreads();
+    Ks = stages + st * STAGE;
+    const __nv_bfloat16* Vs = Ks + TM_K * LD;
+    // every key of the tile is visible to every row of the warp: no mask to apply
+    const bool full = kt >= wlo_last && kt + TM_K - 1 <= p0 + warp * 16;
     if (kt <= whi && kt + TM_K - 1 >= wlo) {       // else: nothing in this tile that a row of this warp sees
       float sc[TM_K / 8][4];
 #pragma unroll
@@ -411,8 +436,8 @@ __global__ void __launch_bounds__(TM_THREADS) softmax_attn_mma_kernel(
           const int rr = e >> 1;
           const int kp = kt + n * 8 + (lane & 3) * 2 + (e & 1);
           float v = sc[n][e] * scale;
-          if (softcap > 0.f) v = softcap * tanhf(v * inv_cap);
-          v = (kp <= qp[rr] && kp >= qlo[rr]) ? v : -INFINITY;
+          if (softcap > 0.f) v = softcap * tm_tanh(v * inv_cap);
+          if (!full) v = (kp <= qp[rr] && kp >= qlo[rr]) ? v : -INFINITY;
           sc[n][e] = v;
           tmax[rr] = fmaxf(tmax[rr], v);
         }
@@ -493,7 +518,13 @@ static int tm_launch(const void* q, int q_stride, const void* gate, int gate_str
                      const float* sink, float scale, float softcap, int B, int Tn, int H, int G, int dim, int vdim, int window, int chunk,
                      int ring, void* y, cudaStream_t st) {
   const dim3 grid((Tn + TM_Q - 1) / TM_Q, H, B);
-  softmax_attn_mma_kernel<D><<<grid, TM_THREADS, 0, st>>>((const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)gate, gate_stride,
+  constexpr int smem = 2 * 2 * TM_K * (D + 8) * (int)sizeof(__nv_bfloat16);
+  static bool sized = false;
+  if (!sized) {
+    LL_CUDA(cudaFuncSetAttribute(softmax_attn_mma_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    sized = true;
+  }
+  softmax_attn_mma_kernel<D><<<grid, TM_THREADS, smem, st>>>((const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)gate, gate_stride,
                                                           (const __nv_bfloat16*)kc, (const __nv_bfloat16*)vc, pos_ids, sink, scale, softcap,
                                                           Tn, H, G, dim, vdim, window, chunk, ring, (__nv_bfloat16*)y);
   LL_LAUNCH_OK("softmax_attn_mma_kernel");

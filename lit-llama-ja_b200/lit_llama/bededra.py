@@ -30,7 +30,7 @@ from .feed_forward import DenseFF
 from .moe import MoE, MoESpec
 from .recurrence import GatedLinearAttention, LinearAttentionSpec, StateSpaceMixer, StateSpaceSpec, pad8
 from .short_conv import ShortConv
-from .stepping import PortionedDecoder, head_logits
+from .stepping import PortionedDecoder, add_norm_pair, head_logits
 from .window_attention import WindowAttention, WindowAttentionSpec
 
 ARCHITECTURE = "Bededra"
@@ -135,16 +135,6 @@ class BededraConfig:
                 raise ValueError(f"layer {i}: unknown feed-forward kind {f.get('kind')!r}")
             layers.append(BededraLayer(kind, mixer, mlp))
         return cls(vocab=vocab, width=width, eps=eps, canon_taps=taps, layers=layers)
-
-
-def add_norm_pair(x, branches, w1, w2, eps, out1, out2, act_dtype) -> None:
-    """``x += sum scale * branch`` in place (fp32); then ``out1 = rmsnorm(x) * w1`` and ``out2 = rmsnorm(x) * w2`` (either
-    may be None).  ``out1`` may be fp32 or the activation dtype."""
-    assert len(branches) <= 3
-    b = list(branches) + [(None, 0.0)] * (3 - len(branches))
-    N.call("ll_add_norm_pair", N.ptr(x), N.ptr(b[0][0]), float(b[0][1]), N.ptr(b[1][0]), float(b[1][1]), N.ptr(b[2][0]), float(b[2][1]),
-           N.ptr(w1), N.ptr(w2), float(eps), N.ptr(out1), 1 if (out1 is not None and out1.dtype == torch.float32) else 0, N.ptr(out2),
-           N.dtype_code(act_dtype), x.shape[0], x.shape[1], N.stream())
 
 
 class ParallelMixer(nn.Module):

@@ -35,16 +35,18 @@ class RotarySpec:
             raise ValueError(f"unknown frequency scaling {self.scaling!r}")
 
     @classmethod
-    def from_dict(cls, rot: Optional[dict]) -> "RotarySpec":
-        """``{"dims", "base", "scaling": {"factor"[, "low", "high", "original"]}}``; None: no rotation."""
+    def from_dict(cls, rot: Optional[dict], head_dim: Optional[int] = None) -> "RotarySpec":
+        """``{"dims", "base", "scaling": {"factor"[, "low", "high", "original"]}}``; None: no rotation.  ``dims`` left out:
+        the whole head (``head_dim``)."""
         if not rot:
             return cls(dims=0)
+        dims = int(rot["dims"]) if rot.get("dims") is not None else int(head_dim)
         sc = rot.get("scaling") or None
         if sc is None:
-            return cls(dims=int(rot["dims"]), base=float(rot["base"]))
+            return cls(dims=dims, base=float(rot["base"]))
         if sc.get("original") is None:
-            return cls(dims=int(rot["dims"]), base=float(rot["base"]), scaling="linear", factor=float(sc["factor"]))
-        return cls(dims=int(rot["dims"]), base=float(rot["base"]), scaling="bands", factor=float(sc["factor"]),
+            return cls(dims=dims, base=float(rot["base"]), scaling="linear", factor=float(sc["factor"]))
+        return cls(dims=dims, base=float(rot["base"]), scaling="bands", factor=float(sc["factor"]),
                    low=float(sc["low"]), high=float(sc["high"]), original=float(sc["original"]))
 
     def frequencies(self, device=None) -> torch.Tensor:

@@ -135,3 +135,13 @@ def head_logits(xn: torch.Tensor, head: torch.Tensor, vocab: int) -> torch.Tenso
         except RuntimeError:           # a width the library's mixed-output GEMM does not take: fp32 product of the same operands
             logits = xn.float() @ head.float().t()
     return logits[:, :vocab]
+
+
+def add_norm_pair(x, branches, w1, w2, eps, out1, out2, act_dtype) -> None:
+    """``x += sum scale * branch`` in place (fp32); then ``out1 = rmsnorm(x) * w1`` and ``out2 = rmsnorm(x) * w2`` (either
+    may be None).  ``out1`` may be fp32 or the activation dtype."""
+    assert len(branches) <= 3
+    b = list(branches) + [(None, 0.0)] * (3 - len(branches))
+    N.call("ll_add_norm_pair", N.ptr(x), N.ptr(b[0][0]), float(b[0][1]), N.ptr(b[1][0]), float(b[1][1]), N.ptr(b[2][0]), float(b[2][1]),
+           N.ptr(w1), N.ptr(w2), float(eps), N.ptr(out1), 1 if (out1 is not None and out1.dtype == torch.float32) else 0, N.ptr(out2),
+           N.dtype_code(act_dtype), x.shape[0], x.shape[1], N.stream())

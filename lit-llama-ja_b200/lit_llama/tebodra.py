@@ -29,13 +29,12 @@ import torch
 import torch.nn as nn
 
 from . import _native as N
-from .bededra import add_norm_pair
 from .cache import TensorPool, max_portion, ring_length
 from .feed_forward import DenseFF
 from .recurrence import MatrixMemoryMixer, MatrixMemorySpec, pad8
 from .rotary import RotarySpec
 from .softmax_attention import SoftmaxAttention, SoftmaxAttentionSpec
-from .stepping import PortionedDecoder, head_logits
+from .stepping import PortionedDecoder, add_norm_pair, head_logits
 
 ARCHITECTURE = "Tebodra"
 
@@ -104,7 +103,8 @@ class TebodraConfig:
                     taps = shapes[p + "q.conv"][1] if p + "q.conv" in shapes else 0
                 mixer = SoftmaxAttentionSpec(
                     width=width, heads=heads, kv_heads=kv_heads, dim=dim, vdim=int(m["vdim"]) if m.get("vdim") is not None else dim,
-                    scale=float(m["scale"]), eps=eps, rotary=RotarySpec.from_dict(m.get("rot")), softcap=float(m.get("softcap") or 0.0),
+                    scale=float(m["scale"]) if m.get("scale") is not None else dim ** -0.5, eps=eps,
+                    rotary=RotarySpec.from_dict(m.get("rot"), dim), softcap=float(m.get("softcap") or 0.0),
                     window=None, chunk=int(mask["size"]) if mask.get("size") is not None else None, sink=second, qk_norm=second,
                     conv_taps=int(taps), own_values=second, kv_from=src)
                 if src is not None:

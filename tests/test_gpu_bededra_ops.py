@@ -316,7 +316,7 @@ def test_plain_gated_experts(M, E, ff, dtype):
 
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_residual_update_and_both_norms(dtype):
-    from lit_llama.bededra import add_norm_pair
+    from lit_llama.stepping import add_norm_pair
 
     r = np.random.RandomState(0)
     M, E = 6, 50
