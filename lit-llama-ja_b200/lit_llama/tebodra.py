@@ -101,12 +101,16 @@ class TebodraConfig:
                 taps = m.get("conv")
                 if taps is None:
                     taps = shapes[p + "q.conv"][1] if p + "q.conv" in shapes else 0
+                # the kind fixes which parts a layer has; where the tensors are known, their presence has the last word
+                has = (lambda name, default: (p + name in shapes) if shapes else default)
+                sink, qk_norm = has("sink", second), has("q.norm", second)
+                own_values = has("v", second) if src is None else layers[src].mixer.own_values
                 mixer = SoftmaxAttentionSpec(
                     width=width, heads=heads, kv_heads=kv_heads, dim=dim, vdim=int(m["vdim"]) if m.get("vdim") is not None else dim,
                     scale=float(m["scale"]) if m.get("scale") is not None else dim ** -0.5, eps=eps,
                     rotary=RotarySpec.from_dict(m.get("rot"), dim), softcap=float(m.get("softcap") or 0.0),
-                    window=None, chunk=int(mask["size"]) if mask.get("size") is not None else None, sink=second, qk_norm=second,
-                    conv_taps=int(taps), own_values=second, kv_from=src)
+                    window=None, chunk=int(mask["size"]) if mask.get("size") is not None else None, sink=sink, qk_norm=qk_norm,
+                    conv_taps=int(taps), own_values=own_values, kv_from=src)
                 if src is not None:
                     o = layers[src].mixer
                     if (o.kv_heads, o.dim, o.vdim) != (mixer.kv_heads, mixer.dim, mixer.vdim):

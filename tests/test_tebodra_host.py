@@ -36,6 +36,8 @@ def test_configuration_from_file_and_from_shapes():
     lean["layers"] = [dict(l, mlp=(None if l["mlp"] is None else {"kind": "dense"})) for l in cfg["layers"]]
     c2 = TebodraConfig.from_dict(lean, {k: v.shape for k, v in W.items()})
     assert (c2.vocab, c2.width, [l.ff for l in c2.layers]) == (c.vocab, c.width, [l.ff for l in c.layers])
+    assert [(l.mixer.sink, l.mixer.qk_norm, l.mixer.own_values) for l in c2.layers if l.kind != "mlstm"] == \
+        [(l.mixer.sink, l.mixer.qk_norm, l.mixer.own_values) for l in c.layers if l.kind != "mlstm"]
     bad = dict(cfg, layers=[dict(cfg["layers"][3])] + cfg["layers"][1:])
     with pytest.raises(ValueError):
         TebodraConfig.from_dict(bad)                                             # kv_from must name an earlier owner
