@@ -22,7 +22,7 @@
 extern "C" {
 #endif
 
-#define LL_ABI_VERSION 14
+#define LL_ABI_VERSION 15
 
 #define LL_OK 0
 #define LL_ERR_ARG (-1)         /* bad shape / dtype / null pointer */
@@ -463,6 +463,24 @@ LL_API int ll_relu_squared(void* h, int dtype, size_t n, ll_stream stream);
 /* h <- gelu(h), in place: 0.5 h (1 + erf(h / sqrt 2)), or with tanh_form 0.5 h (1 + tanh(sqrt(2/pi) (h + 0.044715 h^3))) */
 LL_API int ll_gelu(void* h, int dtype, int tanh_form, size_t n, ll_stream stream);
 
+/* Several copies of the residual stream X [rows][S][dim] fp32 (S <= 8).  write: X'[t] = sum_s mix[s][t] X[s] + out[t] * r * ls * y,
+ * all copies at once from the old ones (mix [S][S] indexed [from][to], NULL: every copy keeps itself; y [rows][dim] in the
+ * activation dtype, NULL: nothing is added; ls fp32 [dim], NULL: none).  read: u = sum_t in[t] X'[t] (in NULL: the plain sum),
+ * h = u / sqrt(mean(u^2) + eps) * w (fp32 when h_f32, else the activation dtype; h NULL: no read).  total (optional): the plain
+ * sum of the new copies, fp32 [rows][dim].  The old copies are read at src + m * src_row + s * src_copy (src_copy 0: every copy
+ * starts as the same row); X may be src. */
+LL_API int ll_hyper_mix_norm(const float* src, long long src_row, long long src_copy, float* X, const void* y, const float* ls, float r,
+                             const float* mix, const float* w_out, const float* w_in, const float* w, float eps, void* h, int h_f32,
+                             float* total, int act_dtype, int rows, int S, int dim, ll_stream stream);
+/* out[m][:] = x[m][:] / sqrt(mean(x[m][:]^2) + eps) * w  (w fp32 [dim] or NULL; rows of x_stride / out_stride elements) */
+LL_API int ll_row_norm(const void* x, int x_stride, const float* w, float eps, void* out, int out_stride, int dtype, int rows, int dim,
+                       ll_stream stream);
+/* out[m][c] = a[m][c] * sigmoid(gate[m][c]), c < C; each operand with its own row stride; out may be a */
+LL_API int ll_sigmoid_gate_mul(const void* a, int a_stride, const void* gate, int gate_stride, void* out, int out_stride, int dtype,
+                               int rows, int C, ll_stream stream);
+/* x <- cap * tanh(x / cap), fp32, in place */
+LL_API int ll_tanh_cap(float* x, float cap, size_t n, ll_stream stream);
+
 /* ---------------------------------------------------------------------------------------
  * Short causal convolution with state (csrc/short_conv.cu)
  * ------------------------------------------------------------------------------------- */
@@ -537,6 +555,22 @@ LL_API int ll_softmax_attn(const void* q, int q_stride, const void* gate, int ga
                            const int32_t* pos_ids, const float* sink, float scale, float softcap, int B, int T, int H, int G, int dim,
                            int vdim, int window, int chunk, int ring, int splits, int form, float* scratch, void* y,
                            ll_stream stream);
+
+/* The same two calls for heads that carry `maps` score maps (1 or 2): the q row holds H heads of [map 0 | map 1] (dim each), the
+ * k row G heads likewise (kc [B][ring][G*maps*dim]), the values stay [G*vdim] and serve every map.  Two maps are combined as
+ * o = a_0 - diff_lambda * a_1, o / sqrt(mean_c(o^2) + eps) * diff_post, before the gate.  sink: [H*maps].  In the append q may be
+ * NULL (keys and values only); values taken from the keys need maps == 1.  The fp32 form needs scratch
+ * (ll_softmax_attn_scratch_bytes(M, H*maps, vdim, splits)) whenever maps > 1; ll_softmax_attn_tensor_form() tells whether a call
+ * with form 0 takes the tensor-core form, which needs none. */
+LL_API int ll_qk_rotary_append_maps(const void* q, int q_stride, const void* k, int k_stride, const void* v, int v_stride, int dtype,
+                                    const float* q_norm, const float* k_norm, float eps, const float* freq, int rot_dims,
+                                    const int32_t* pos_ids, void* q_out, void* kc, void* vc, int B, int T, int H, int G, int dim,
+                                    int vdim, int ring, int maps, ll_stream stream);
+LL_API int ll_softmax_attn_tensor_form(int dtype, int T, int dim, int vdim, int q_stride, int gate_stride, int splits);
+LL_API int ll_softmax_attn_maps(const void* q, int q_stride, const void* gate, int gate_stride, const void* kc, const void* vc, int dtype,
+                                const int32_t* pos_ids, const float* sink, float scale, float softcap, int B, int T, int H, int G,
+                                int dim, int vdim, int window, int chunk, int ring, int splits, int form, int maps, float diff_lambda,
+                                float diff_post, float eps, float* scratch, void* y, ll_stream stream);
 
 #ifdef __cplusplus
 }

@@ -24,6 +24,7 @@ FAMILY_SOURCES = {
     "Lepalorn": ["quant_pack", "decode_ops", "sampling", "residual_ops", "latent_attn", "moe_ops", "moe_gemm_tc"],
     "Bededra": ["quant_pack", "residual_ops", "short_conv", "decay_scan", "window_attn", "moe_ops", "moe_gemm_tc"],
     "Tebodra": ["quant_pack", "residual_ops", "short_conv", "decay_scan", "rotary_attn"],
+    "Bumulix": ["quant_pack", "residual_ops", "rotary_attn", "latent_attn"],
 }
 
 

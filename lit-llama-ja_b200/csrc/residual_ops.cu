@@ -257,9 +257,195 @@ __global__ void gelu_kernel(T* __restrict__ h, int tanh_form, size_t n) {
   dt<T>::st(h, i, r);
 }
 
+// Several copies of the residual stream ("hyper-connections"): X [rows][S][dim] fp32.  One launch closes a sublayer and opens
+// the next:
+//   write   X'[t] = sum_s mix[s][t] X[s] + out[t] * r * ls * y      all S copies at once from the old ones (mix [S][S] indexed
+//           [from][to], NULL: every copy keeps itself; y the sublayer's result in the activation dtype, NULL: nothing is added;
+//           ls a per-channel scale of y, NULL: none)
+//   read    u = sum_t in[t] X'[t] (in NULL: the plain sum);  h = u / sqrt(mean(u^2) + eps) * w      (h NULL: no read)
+//   total   (optional) the plain sum of the new copies, fp32 [rows][dim]
+// The old copies are read at src + m * src_row + s * src_copy (src_copy 0: every copy starts as the same row, the embedding
+// output); when src is X itself and nothing is added or mixed, nothing is written.
+template <typename TA, int SMAX>
+__global__ void hyper_mix_norm_kernel(const float* src, long long src_row, long long src_copy, float* X, const TA* __restrict__ y,
+                                      const float* __restrict__ ls, float r, const float* __restrict__ mix,
+                                      const float* __restrict__ w_out, const float* __restrict__ w_in, const float* __restrict__ w,
+                                      float eps, void* __restrict__ h, int h_f32, float* __restrict__ total, int S, int dim) {
+  extern __shared__ float hyper_us[];            // the row of u
+  __shared__ float red[32];
+  __shared__ float cm[SMAX * SMAX], co[SMAX], ci[SMAX];
+  for (int i = threadIdx.x; i < S * S; i += blockDim.x) cm[i] = mix ? mix[i] : 0.f;
+  for (int i = threadIdx.x; i < S; i += blockDim.x) co[i] = w_out ? w_out[i] : 1.f, ci[i] = w_in ? w_in[i] : 1.f;
+  __syncthreads();
+  const size_t m = blockIdx.x;
+  const bool write = y || mix || src != X || src_row != (long long)S * dim || src_copy != dim;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < dim; i += blockDim.x) {
+    float xs[SMAX];
+#pragma unroll
+    for (int s = 0; s < SMAX; ++s) xs[s] = s < S ? src[m * src_row + s * src_copy + i] : 0.f;
+    float yv = 0.f;
+    if (y) {
+      yv = dt<TA>::ld(y, m * dim + i);
+      if (ls) yv *= ls[i];
+      yv *= r;
+    }
+    float u = 0.f, tot = 0.f;
+#pragma unroll
+    for (int t = 0; t < SMAX; ++t) {
+      if (t >= S) break;
+      float xt = xs[t];
+      if (mix) {
+        xt = 0.f;
+#pragma unroll
+        for (int s = 0; s < SMAX; ++s)
+          if (s < S) xt = fmaf(cm[s * S + t], xs[s], xt);
+      }
+      if (y) xt = fmaf(co[t], yv, xt);
+      if (write) X[(m * S + t) * dim + i] = xt;
+      u = fmaf(ci[t], xt, u);
+      tot += xt;
+    }
+    if (total) total[m * dim + i] = tot;
+    hyper_us[i] = u;
+    ss += u * u;
+  }
+  if (!h) return;
+  ss = block_sum(ss, red);
+  const float k = 1.f / sqrtf(ss / (float)dim + eps);
+  for (int i = threadIdx.x; i < dim; i += blockDim.x) {
+    const float n = hyper_us[i] * k * w[i];
+    if (h_f32) ((float*)h)[m * dim + i] = n;
+    else dt<TA>::st((TA*)h, m * dim + i, n);
+  }
+}
+
+// out[m][:] = x[m][:] / sqrt(mean(x[m][:]^2) + eps) * w      (rows of x_stride / out_stride elements; w fp32 or NULL)
+template <typename T>
+__global__ void row_norm_kernel(const T* __restrict__ x, int x_stride, const float* __restrict__ w, float eps, T* __restrict__ out,
+                                int out_stride, int dim) {
+  __shared__ float red[32];
+  const T* xr = x + (size_t)blockIdx.x * x_stride;
+  T* orow = out + (size_t)blockIdx.x * out_stride;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < dim; i += blockDim.x) {
+    const float v = dt<T>::ld(xr, i);
+    ss += v * v;
+  }
+  ss = block_sum(ss, red);
+  const float k = 1.f / sqrtf(ss / (float)dim + eps);
+  for (int i = threadIdx.x; i < dim; i += blockDim.x) dt<T>::st(orow, i, dt<T>::ld(xr, i) * k * (w ? w[i] : 1.f));
+}
+
+// out[m][c] = a[m][c] * sigmoid(gate[m][c])     (each with its own row stride; out may be a)
+template <typename T>
+__global__ void sigmoid_gate_mul_kernel(const T* a, int a_stride, const T* __restrict__ gate, int gate_stride, T* out, int out_stride,
+                                        int C, size_t n) {
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const size_t m = i / C, c = i - m * C;
+  const float g = dt<T>::ld(gate, m * gate_stride + c);
+  dt<T>::st(out, m * out_stride + c, dt<T>::ld(a, m * a_stride + c) / (1.f + expf(-g)));
+}
+
+// in place: cap * tanh(v / cap)
+__global__ void tanh_cap_kernel(float* __restrict__ x, float cap, float inv_cap, size_t n) {
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) x[i] = cap * tanhf(x[i] * inv_cap);
+}
+
 }  // namespace llb
 
 extern "C" {
+
+int ll_hyper_mix_norm(const float* src, long long src_row, long long src_copy, float* X, const void* y, const float* ls, float r,
+                      const float* mix, const float* w_out, const float* w_in, const float* w, float eps, void* h, int h_f32,
+                      float* total, int act_dtype, int rows, int S, int dim, ll_stream stream) {
+  LL_CHECK_ARG(src && X && rows >= 0 && S >= 1 && dim > 0 && (!h || w) && (!y || w_out), "bad hyper_mix_norm arguments");
+  if (S > 8) {
+    set_error("hyper_mix_norm: %d copies of the stream (up to 8)", S);
+    return LL_ERR_UNSUPPORTED;
+  }
+  if (rows == 0) return LL_OK;
+  cudaStream_t st = (cudaStream_t)stream;
+  const int threads = dim >= 2048 ? 512 : dim >= 512 ? 256 : 128;
+  const size_t smem = (size_t)dim * sizeof(float);
+  if (smem > 200 * 1024) {
+    set_error("hyper_mix_norm: rows of %d numbers", dim);
+    return LL_ERR_UNSUPPORTED;
+  }
+#define LL_HYPER(TA, SM)                                                                                                            \
+  {                                                                                                                                 \
+    static bool sized = false;                                                                                                      \
+    if (!sized && smem > 48 * 1024) {                                                                                               \
+      LL_CUDA(cudaFuncSetAttribute(hyper_mix_norm_kernel<TA, SM>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));        \
+      sized = true;                                                                                                                 \
+    }                                                                                                                               \
+    hyper_mix_norm_kernel<TA, SM><<<rows, threads, smem, st>>>(src, src_row, src_copy, X, (const TA*)y, ls, r, mix, w_out, w_in, w, eps, \
+                                                              h, h_f32, total, S, dim);                                             \
+  }
+#define LL_HYPER_S(TA)                                                                                                              \
+  if (S == 1) LL_HYPER(TA, 1) else if (S == 2) LL_HYPER(TA, 2) else if (S <= 4) LL_HYPER(TA, 4) else LL_HYPER(TA, 8)
+  if (act_dtype == LL_F32) {
+    LL_HYPER_S(float)
+  } else if (act_dtype == LL_BF16) {
+    LL_HYPER_S(__nv_bfloat16)
+  } else {
+    set_error("hyper_mix_norm: unsupported dtype %d", act_dtype);
+    return LL_ERR_UNSUPPORTED;
+  }
+#undef LL_HYPER_S
+#undef LL_HYPER
+  LL_LAUNCH_OK("hyper_mix_norm_kernel");
+  return LL_OK;
+}
+
+int ll_row_norm(const void* x, int x_stride, const float* w, float eps, void* out, int out_stride, int dtype, int rows, int dim,
+                ll_stream stream) {
+  LL_CHECK_ARG(x && out && rows >= 0 && dim > 0 && x_stride >= dim && out_stride >= dim, "bad row_norm arguments");
+  if (rows == 0) return LL_OK;
+  cudaStream_t st = (cudaStream_t)stream;
+  const int threads = dim >= 1024 ? 256 : dim >= 256 ? 128 : 64;
+  if (dtype == LL_F32) row_norm_kernel<float><<<rows, threads, 0, st>>>((const float*)x, x_stride, w, eps, (float*)out, out_stride, dim);
+  else if (dtype == LL_BF16)
+    row_norm_kernel<__nv_bfloat16><<<rows, threads, 0, st>>>((const __nv_bfloat16*)x, x_stride, w, eps, (__nv_bfloat16*)out, out_stride,
+                                                            dim);
+  else {
+    set_error("row_norm: unsupported dtype %d", dtype);
+    return LL_ERR_UNSUPPORTED;
+  }
+  LL_LAUNCH_OK("row_norm_kernel");
+  return LL_OK;
+}
+
+int ll_sigmoid_gate_mul(const void* a, int a_stride, const void* gate, int gate_stride, void* out, int out_stride, int dtype, int rows,
+                        int C, ll_stream stream) {
+  LL_CHECK_ARG(a && gate && out && rows >= 0 && C > 0, "bad sigmoid_gate_mul arguments");
+  const size_t n = (size_t)rows * C;
+  if (n == 0) return LL_OK;
+  cudaStream_t st = (cudaStream_t)stream;
+  const unsigned blocks = (unsigned)((n + 255) / 256);
+  if (dtype == LL_F32)
+    sigmoid_gate_mul_kernel<float><<<blocks, 256, 0, st>>>((const float*)a, a_stride, (const float*)gate, gate_stride, (float*)out,
+                                                          out_stride, C, n);
+  else if (dtype == LL_BF16)
+    sigmoid_gate_mul_kernel<__nv_bfloat16><<<blocks, 256, 0, st>>>((const __nv_bfloat16*)a, a_stride, (const __nv_bfloat16*)gate,
+                                                                  gate_stride, (__nv_bfloat16*)out, out_stride, C, n);
+  else {
+    set_error("sigmoid_gate_mul: unsupported dtype %d", dtype);
+    return LL_ERR_UNSUPPORTED;
+  }
+  LL_LAUNCH_OK("sigmoid_gate_mul_kernel");
+  return LL_OK;
+}
+
+int ll_tanh_cap(float* x, float cap, size_t n, ll_stream stream) {
+  LL_CHECK_ARG(x && cap > 0.f, "bad tanh_cap arguments");
+  if (n == 0) return LL_OK;
+  tanh_cap_kernel<<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>(x, cap, 1.f / cap, n);
+  LL_LAUNCH_OK("tanh_cap_kernel");
+  return LL_OK;
+}
 
 int ll_add_norm_pair(float* x, const void* a0, float s0, const void* a1, float s1, const void* a2, float s2, const float* w1,
                      const float* w2, float eps, void* out1, int out1_f32, void* out2, int act_dtype, int rows, int dim,

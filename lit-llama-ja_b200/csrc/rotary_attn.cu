@@ -10,6 +10,11 @@
 //
 // Query head h reads key / value head g = h / (H / G).  Scores, softmax and the weighted sums are fp32 in every form; the
 // tensor-core form (prompts in bf16) rounds the softmax weights to bf16 as the operand of P.V, which is the only place.
+//
+//   maps      a head may carry `maps` score maps (1 or 2): its query row is [map 0 | map 1] (dim each), the key row of head g
+//             likewise, and every map is a softmax attention of its own over the SAME value row of head g.  Two maps are
+//             combined as a difference, o = a_0 - lambda * a_1, then divided by the root mean square of o over the head's
+//             values (eps inside the root) and multiplied by `post`; the gate, if any, follows.
 #include "common.cuh"
 
 namespace llb {
@@ -73,16 +78,17 @@ __global__ void __launch_bounds__(QP_THREADS) qk_rotary_append_kernel(
     const T* __restrict__ q, int q_stride, const T* __restrict__ k, int k_stride, const T* __restrict__ v, int v_stride,
     const float* __restrict__ q_norm, const float* __restrict__ k_norm, float eps, const float* __restrict__ freq, int rot_dims,
     const int32_t* __restrict__ pos_ids, T* __restrict__ q_out, T* __restrict__ kc, T* __restrict__ vc, int Tn, int H, int G, int dim,
-    int vdim, int ring) {
+    int vdim, int ring, int maps) {
   __shared__ float red[32];
   const int m = blockIdx.x, b = m / Tn, t = m - b * Tn;
   const int p = pos_ids[t];
   const float pos = (float)p;
-  qp_row<T>(q + (size_t)m * q_stride, q_norm, eps, freq, rot_dims, pos, H, dim, q_out + (size_t)m * H * dim, nullptr, red);
+  const int HM = H * maps, GM = G * maps;      // head rows of the q and k projections; the values have G
+  if (q) qp_row<T>(q + (size_t)m * q_stride, q_norm, eps, freq, rot_dims, pos, HM, dim, q_out + (size_t)m * HM * dim, nullptr, red);
   if (!k) return;
   const size_t slot = (size_t)b * ring + (size_t)(p % ring);
   T* vrow = vc + slot * (size_t)G * vdim;
-  qp_row<T>(k + (size_t)m * k_stride, k_norm, eps, freq, rot_dims, pos, G, dim, kc + slot * (size_t)G * dim, v ? nullptr : vrow, red);
+  qp_row<T>(k + (size_t)m * k_stride, k_norm, eps, freq, rot_dims, pos, GM, dim, kc + slot * (size_t)GM * dim, v ? nullptr : vrow, red);
   if (v)
     for (int i = threadIdx.x; i < G * vdim; i += blockDim.x) vrow[i] = v[(size_t)m * v_stride + i];
 }
@@ -94,6 +100,12 @@ __global__ void __launch_bounds__(QP_THREADS) qk_rotary_append_kernel(
 // leaving its (max, sum, weighted sum) in scratch for the merge kernel: decoding one token over a long cache then fills the
 // device.
 constexpr int SA_WARPS = 4;
+
+// score maps per head and how two of them meet: o = a_0 - lambda * a_1, o / sqrt(mean(o^2) + eps) * post
+struct DiffMaps {
+  int maps;
+  float lambda, post, eps;
+};
 
 template <typename T>
 __device__ __forceinline__ void sa_load8(const T* __restrict__ row, int e0, int n, bool vec, float (&o)[8]);
@@ -133,12 +145,15 @@ template <typename T, int R, int RV>
 __global__ void __launch_bounds__(SA_WARPS * 32) softmax_attn_kernel(
     const T* __restrict__ q, int q_stride, const T* __restrict__ gate, int gate_stride, const T* __restrict__ kc, const T* __restrict__ vc,
     const int32_t* __restrict__ pos_ids, const float* __restrict__ sink, float scale, float softcap, int Tn, int H, int G, int dim,
-    int vdim, int window, int chunk, int ring, int splits, int pairs, float* __restrict__ part_ml, float* __restrict__ part_acc,
-    T* __restrict__ y) {
+    int vdim, int window, int chunk, int ring, int splits, int maps, int pairs, float* __restrict__ part_ml,
+    float* __restrict__ part_acc, T* __restrict__ y) {
+  // a warp owns one (query, head, map); with one map per head, h below is the head itself
   const int pair = blockIdx.x * SA_WARPS + (threadIdx.x >> 5);
   if (pair >= pairs) return;
   const int lane = threadIdx.x & 31, grp = lane >> 3, sub = lane & 7;
-  const int m = pair / H, h = pair - m * H, g = h / (H / G);
+  const int HM = H * maps;
+  const int m = pair / HM, h = pair - m * HM, head = h / maps, g = head / (H / G);
+  const int GK = G * maps, gk = g * maps + (h - head * maps);
   const int b = m / Tn, t = m - b * Tn;
   const int i = pos_ids[t];
   const int lo = sa_first_visible(i, window, chunk);
@@ -157,12 +172,12 @@ __global__ void __launch_bounds__(SA_WARPS * 32) softmax_attn_kernel(
     for (int e = 0; e < 8; ++e) acc[r][e] = 0.f;
   float mx = -INFINITY, l = 0.f;
   const float inv_cap = softcap > 0.f ? 1.f / softcap : 0.f;
-  const T* kbase = kc + ((size_t)b * ring * G + g) * dim;
+  const T* kbase = kc + ((size_t)b * ring * GK + gk) * dim;
   const T* vbase = vc + ((size_t)b * ring * G + g) * vdim;
   const unsigned gmask = 0xffu << (grp * 8);
   for (int j = j0 + grp; j < j1; j += 4) {
     const size_t slot = (size_t)(j % ring);
-    const T* krow = kbase + slot * G * dim;
+    const T* krow = kbase + slot * GK * dim;
     float s = 0.f;
 #pragma unroll
     for (int r = 0; r < R; ++r) {
@@ -207,7 +222,7 @@ __global__ void __launch_bounds__(SA_WARPS * 32) softmax_attn_kernel(
       }
     mx = mn;
   }
-  if (splits > 1) {
+  if (splits > 1 || maps > 1) {                  // several maps meet in the merge kernel, also when the keys are not split
     const size_t at = (size_t)pair * splits + blockIdx.y;
     if (lane == 0) part_ml[at * 2] = mx, part_ml[at * 2 + 1] = l;
     if (grp == 0) {
@@ -247,30 +262,56 @@ __global__ void __launch_bounds__(SA_WARPS * 32) softmax_attn_kernel(
     }
 }
 
-// Merge of the key ranges of one (query, head), in order; a warp per pair, a lane per value dimension.
+// Merge of the key ranges of one (query, head), in order; a warp per pair, a lane per value dimension.  With two maps per
+// head the warp merges both and combines them: o = a_0 - lambda * a_1, o / sqrt(mean(o^2) + eps) * post.
 template <typename T>
 __global__ void softmax_attn_merge_kernel(const float* __restrict__ part_ml, const float* __restrict__ part_acc,
                                           const T* __restrict__ gate, int gate_stride, const float* __restrict__ sink, int H, int vdim,
-                                          int splits, int pairs, T* __restrict__ y) {
-  const int pair = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+                                          int splits, int maps, float lambda, float post, float eps, int pairs, T* __restrict__ y) {
+  const int pair = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);      // (query, head)
   if (pair >= pairs) return;
   const int lane = threadIdx.x & 31;
   const int m = pair / H, h = pair - m * H;
-  float mx = sink ? sink[h] : -INFINITY;
-  for (int s = 0; s < splits; ++s) mx = fmaxf(mx, part_ml[((size_t)pair * splits + s) * 2]);
-  float den = sink ? expf(sink[h] - mx) : 0.f;
-  for (int s = 0; s < splits; ++s) {
-    const float ms = part_ml[((size_t)pair * splits + s) * 2];
-    if (ms != -INFINITY) den += part_ml[((size_t)pair * splits + s) * 2 + 1] * expf(ms - mx);
-  }
-  const float inv = 1.f / den;
-  for (int c = lane; c < vdim; c += 32) {
-    float o = 0.f;
+  float ov[8];                                   // vdim <= 256: up to eight values per lane
+#pragma unroll
+  for (int e = 0; e < 8; ++e) ov[e] = 0.f;
+  for (int mp = 0; mp < maps; ++mp) {
+    const size_t sp = (size_t)pair * maps + mp;  // the (query, head, map) the attention kernel numbered
+    const float* snk = sink ? sink + (size_t)h * maps + mp : nullptr;
+    float mx = snk ? *snk : -INFINITY;
+    for (int s = 0; s < splits; ++s) mx = fmaxf(mx, part_ml[(sp * splits + s) * 2]);
+    float den = snk ? expf(*snk - mx) : 0.f;
     for (int s = 0; s < splits; ++s) {
-      const float ms = part_ml[((size_t)pair * splits + s) * 2];
-      if (ms != -INFINITY) o += part_acc[((size_t)pair * splits + s) * vdim + c] * expf(ms - mx);
+      const float ms = part_ml[(sp * splits + s) * 2];
+      if (ms != -INFINITY) den += part_ml[(sp * splits + s) * 2 + 1] * expf(ms - mx);
     }
-    o *= inv;
+    const float inv = 1.f / den;
+    const float wgt = mp == 0 ? 1.f : -lambda;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      const int c = lane + e * 32;
+      if (c >= vdim) continue;
+      float o = 0.f;
+      for (int s = 0; s < splits; ++s) {
+        const float ms = part_ml[(sp * splits + s) * 2];
+        if (ms != -INFINITY) o += part_acc[(sp * splits + s) * vdim + c] * expf(ms - mx);
+      }
+      ov[e] += wgt * (o * inv);
+    }
+  }
+  float k = 1.f;
+  if (maps > 1) {
+    float ss = 0.f;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) ss += ov[e] * ov[e];
+    ss = warp_sum(ss);
+    k = post / sqrtf(ss / (float)vdim + eps);
+  }
+#pragma unroll
+  for (int e = 0; e < 8; ++e) {
+    const int c = lane + e * 32;
+    if (c >= vdim) break;
+    float o = ov[e] * k;
     if (gate) o *= 1.f / (1.f + expf(-dt<T>::ld(gate, (size_t)m * gate_stride + (size_t)h * vdim + c)));
     dt<T>::st(y, (size_t)m * H * vdim + (size_t)h * vdim + c, o);
   }
@@ -279,18 +320,20 @@ __global__ void softmax_attn_merge_kernel(const float* __restrict__ part_ml, con
 template <typename T, int R, int RV>
 static int sa_launch(const void* q, int q_stride, const void* gate, int gate_stride, const void* kc, const void* vc,
                      const int32_t* pos_ids, const float* sink, float scale, float softcap, int B, int Tn, int H, int G, int dim,
-                     int vdim, int window, int chunk, int ring, int splits, float* scratch, void* y, cudaStream_t st) {
-  const int pairs = B * Tn * H;
+                     int vdim, int window, int chunk, int ring, int splits, const DiffMaps& dm, float* scratch, void* y,
+                     cudaStream_t st) {
+  const int pairs = B * Tn * H * dm.maps;
   float* part_ml = scratch;
   float* part_acc = scratch ? scratch + (size_t)pairs * splits * 2 : nullptr;
   const dim3 grid((pairs + SA_WARPS - 1) / SA_WARPS, splits);
   softmax_attn_kernel<T, R, RV><<<grid, SA_WARPS * 32, 0, st>>>((const T*)q, q_stride, (const T*)gate, gate_stride, (const T*)kc,
                                                                (const T*)vc, pos_ids, sink, scale, softcap, Tn, H, G, dim, vdim, window,
-                                                               chunk, ring, splits, pairs, part_ml, part_acc, (T*)y);
+                                                               chunk, ring, splits, dm.maps, pairs, part_ml, part_acc, (T*)y);
   LL_LAUNCH_OK("softmax_attn_kernel");
-  if (splits > 1) {
-    softmax_attn_merge_kernel<T><<<(pairs + 3) / 4, 128, 0, st>>>(part_ml, part_acc, (const T*)gate, gate_stride, sink, H, vdim, splits,
-                                                                 pairs, (T*)y);
+  if (splits > 1 || dm.maps > 1) {
+    const int heads = B * Tn * H;
+    softmax_attn_merge_kernel<T><<<(heads + 3) / 4, 128, 0, st>>>(part_ml, part_acc, (const T*)gate, gate_stride, sink, H, vdim, splits,
+                                                                 dm.maps, dm.lambda, dm.post, dm.eps, heads, (T*)y);
     LL_LAUNCH_OK("softmax_attn_merge_kernel");
   }
   return LL_OK;
@@ -299,12 +342,13 @@ static int sa_launch(const void* q, int q_stride, const void* gate, int gate_str
 template <typename T>
 static int sa_dispatch(const void* q, int q_stride, const void* gate, int gate_stride, const void* kc, const void* vc,
                        const int32_t* pos_ids, const float* sink, float scale, float softcap, int B, int Tn, int H, int G, int dim,
-                       int vdim, int window, int chunk, int ring, int splits, float* scratch, void* y, cudaStream_t st) {
+                       int vdim, int window, int chunk, int ring, int splits, const DiffMaps& dm, float* scratch, void* y,
+                       cudaStream_t st) {
   const int r = dim <= 64 ? 1 : dim <= 128 ? 2 : 4, rv = vdim <= 64 ? 1 : vdim <= 128 ? 2 : 4;
 #define LL_SA(RR, RRV)                                                                                                              \
   if (r == RR && rv == RRV)                                                                                                         \
     return sa_launch<T, RR, RRV>(q, q_stride, gate, gate_stride, kc, vc, pos_ids, sink, scale, softcap, B, Tn, H, G, dim, vdim, window, \
-                                 chunk, ring, splits, scratch, y, st);
+                                 chunk, ring, splits, dm, scratch, y, st);
   LL_SA(1, 1) LL_SA(1, 2) LL_SA(1, 4) LL_SA(2, 1) LL_SA(2, 2) LL_SA(2, 4) LL_SA(4, 1) LL_SA(4, 2) LL_SA(4, 4)
 #undef LL_SA
   return LL_ERR_UNSUPPORTED;
@@ -345,12 +389,14 @@ __device__ __forceinline__ void tm_split2(float x0, float x1, uint32_t& hi, uint
 // 1e-4 for arguments of 1e-3: far below the 2^-9 of the bf16 operands this form works on)
 __device__ __forceinline__ float tm_tanh(float x) { return 1.f - __fdividef(2.f, 1.f + __expf(2.f * x)); }
 
-template <int D>
-__global__ void __launch_bounds__(TM_THREADS, 3) softmax_attn_mma_kernel(
+// MAPS = 2: the block walks its keys once per map (queries and keys of the map, the same values) and keeps the first map's
+// normalised output in registers until the second is there; the difference, its unit norm and `post` are the epilogue.
+template <int D, int MAPS>
+__global__ void __launch_bounds__(TM_THREADS, MAPS == 1 ? 3 : 2) softmax_attn_mma_kernel(
     const __nv_bfloat16* __restrict__ q, int q_stride, const __nv_bfloat16* __restrict__ gate, int gate_stride,
     const __nv_bfloat16* __restrict__ kc, const __nv_bfloat16* __restrict__ vc, const int32_t* __restrict__ pos_ids,
     const float* __restrict__ sink, float scale, float softcap, int Tn, int H, int G, int dim, int vdim, int window, int chunk, int ring,
-    __nv_bfloat16* __restrict__ y) {
+    float lambda, float post, float eps, __nv_bfloat16* __restrict__ y) {
   constexpr int LD = D + 8, CH = D / 8, STAGE = 2 * TM_K * LD;      // a stage: 64 key rows, then 64 value rows
   extern __shared__ __align__(16) unsigned char tm_smem[];
   __nv_bfloat16* const stages = (__nv_bfloat16*)tm_smem;
@@ -361,10 +407,23 @@ __global__ void __launch_bounds__(TM_THREADS, 3) softmax_attn_mma_kernel(
   const int nq = min(TM_Q, Tn - t0);
   const int p0 = pos_ids[t0];                    // a step's positions are consecutive
   const uint4 zero4 = make_uint4(0u, 0u, 0u, 0u);
+  const int qp[2] = {p0 + warp * 16 + (lane >> 2), p0 + warp * 16 + (lane >> 2) + 8};
+  const int qlo[2] = {sa_first_visible(qp[0], window, chunk), sa_first_visible(qp[1], window, chunk)};
+  const int wlo = sa_first_visible(p0 + warp * 16, window, chunk), whi = p0 + warp * 16 + 15;     // what the warp's rows can see
+  const int khi = p0 + nq - 1;
+  const float inv_cap = softcap > 0.f ? 1.f / softcap : 0.f;
+  const int wlo_last = sa_first_visible(whi, window, chunk);
+  const int kt0 = sa_first_visible(p0, window, chunk);
+  const __nv_bfloat16* vbase = vc + ((size_t)b * ring * G + g) * vdim;
+  float first[MAPS == 1 ? 1 : D / 8][4];         // the first map's output, rows and columns as in o
+#pragma unroll 1
+  for (int mp = 0; mp < MAPS; ++mp) {
+  const int hq = h * MAPS + mp, GK = G * MAPS;
+  Ks = stages;
   for (int c = tid; c < TM_Q * CH; c += TM_THREADS) {
     const int r = c / CH, ch = c - r * CH;
     uint4 val = zero4;
-    if (r < nq && ch * 8 < dim) val = *(const uint4*)(q + ((size_t)b * Tn + t0 + r) * q_stride + (size_t)h * dim + ch * 8);
+    if (r < nq && ch * 8 < dim) val = *(const uint4*)(q + ((size_t)b * Tn + t0 + r) * q_stride + (size_t)hq * dim + ch * 8);
     *(uint4*)&Ks[r * LD + ch * 8] = val;
   }
   __syncthreads();
@@ -376,13 +435,7 @@ __global__ void __launch_bounds__(TM_THREADS, 3) softmax_attn_mma_kernel(
 #pragma unroll
   for (int n = 0; n < D / 8; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
   float mrow[2] = {-INFINITY, -INFINITY}, lrow[2] = {0.f, 0.f};
-  const int qp[2] = {p0 + warp * 16 + (lane >> 2), p0 + warp * 16 + (lane >> 2) + 8};
-  const int qlo[2] = {sa_first_visible(qp[0], window, chunk), sa_first_visible(qp[1], window, chunk)};
-  const int wlo = sa_first_visible(p0 + warp * 16, window, chunk), whi = p0 + warp * 16 + 15;     // what the warp's rows can see
-  const int khi = p0 + nq - 1;
-  const float inv_cap = softcap > 0.f ? 1.f / softcap : 0.f;
-  const __nv_bfloat16* kbase = kc + ((size_t)b * ring * G + g) * dim;
-  const __nv_bfloat16* vbase = vc + ((size_t)b * ring * G + g) * vdim;
+  const __nv_bfloat16* kbase = kc + ((size_t)b * ring * GK + (g * MAPS + mp)) * dim;
   // the next tile's rows are copied under the current tile's math: two stages, one cp.async group per tile
   auto load_tile = [&](int kt, int st) {
     __nv_bfloat16* Kd = stages + st * STAGE;
@@ -391,15 +444,13 @@ __global__ void __launch_bounds__(TM_THREADS, 3) softmax_attn_mma_kernel(
       const int r = c / CH, ch = c - r * CH;
       const int j = kt + r;
       const size_t slot = (size_t)(j % ring);
-      if (j <= khi && ch * 8 < dim) tm_cp_async16(&Kd[r * LD + ch * 8], kbase + slot * G * dim + ch * 8);
+      if (j <= khi && ch * 8 < dim) tm_cp_async16(&Kd[r * LD + ch * 8], kbase + slot * GK * dim + ch * 8);
       else *(uint4*)&Kd[r * LD + ch * 8] = zero4;
       if (j <= khi && ch * 8 < vdim) tm_cp_async16(&Vd[r * LD + ch * 8], vbase + slot * G * vdim + ch * 8);
       else *(uint4*)&Vd[r * LD + ch * 8] = zero4;
     }
     asm volatile("cp.async.commit_group;" ::: "memory");
   };
-  const int wlo_last = sa_first_visible(whi, window, chunk);
-  const int kt0 = sa_first_visible(p0, window, chunk);
   load_tile(kt0, 0);
   int st = 0;
   for (int kt = kt0; kt <= khi; kt += TM_K, st ^= 1) {
@@ -482,20 +533,49 @@ __global__ void __launch_bounds__(TM_THREADS, 3) softmax_attn_mma_kernel(
     }
     __syncthreads();
   }
+  float fin[2];
 #pragma unroll
   for (int rr = 0; rr < 2; ++rr) {
     lrow[rr] += __shfl_xor_sync(0xffffffffu, lrow[rr], 1);
     lrow[rr] += __shfl_xor_sync(0xffffffffu, lrow[rr], 2);
-    const int r = warp * 16 + (lane >> 2) + rr * 8;
-    if (r >= nq) continue;
     float den = lrow[rr], c1 = 1.f;
     if (sink) {
-      const float sk = sink[h];
+      const float sk = sink[hq];
       const float mn = fmaxf(mrow[rr], sk);
       c1 = expf(mrow[rr] - mn);
       den = lrow[rr] * c1 + expf(sk - mn);
     }
-    const float f = c1 / den;
+    fin[rr] = den > 0.f ? c1 / den : 0.f;
+  }
+  if (MAPS == 2) {
+    if (mp == 0) {
+#pragma unroll
+      for (int n = 0; n < D / 8; ++n)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) first[MAPS == 1 ? 0 : n][e] = o[n][e] * fin[e >> 1];
+      continue;                                  // (the loop's last barrier has passed: stage 0 is free for the next queries)
+    }
+    float ss[2] = {0.f, 0.f};
+#pragma unroll
+    for (int n = 0; n < D / 8; ++n)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float d = first[MAPS == 1 ? 0 : n][e] - lambda * (o[n][e] * fin[e >> 1]);
+        o[n][e] = d;                             // columns from vdim on hold zeros: the value rows are zero-filled there
+        ss[e >> 1] += d * d;
+      }
+#pragma unroll
+    for (int rr = 0; rr < 2; ++rr) {
+      ss[rr] += __shfl_xor_sync(0xffffffffu, ss[rr], 1);
+      ss[rr] += __shfl_xor_sync(0xffffffffu, ss[rr], 2);
+      fin[rr] = post / sqrtf(ss[rr] / (float)vdim + eps);
+    }
+  }
+#pragma unroll
+  for (int rr = 0; rr < 2; ++rr) {
+    const int r = warp * 16 + (lane >> 2) + rr * 8;
+    if (r >= nq) continue;
+    const float f = fin[rr];
     const size_t m = (size_t)b * Tn + t0 + r;
 #pragma unroll
     for (int n = 0; n < D / 8; ++n) {
@@ -511,22 +591,23 @@ __global__ void __launch_bounds__(TM_THREADS, 3) softmax_attn_mma_kernel(
       }
     }
   }
+  }  // maps
 }
 
-template <int D>
+template <int D, int MAPS>
 static int tm_launch(const void* q, int q_stride, const void* gate, int gate_stride, const void* kc, const void* vc, const int32_t* pos_ids,
                      const float* sink, float scale, float softcap, int B, int Tn, int H, int G, int dim, int vdim, int window, int chunk,
-                     int ring, void* y, cudaStream_t st) {
+                     int ring, const DiffMaps& dm, void* y, cudaStream_t st) {
   const dim3 grid((Tn + TM_Q - 1) / TM_Q, H, B);
   constexpr int smem = 2 * 2 * TM_K * (D + 8) * (int)sizeof(__nv_bfloat16);
   static bool sized = false;
   if (!sized) {
-    LL_CUDA(cudaFuncSetAttribute(softmax_attn_mma_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    LL_CUDA(cudaFuncSetAttribute(softmax_attn_mma_kernel<D, MAPS>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     sized = true;
   }
-  softmax_attn_mma_kernel<D><<<grid, TM_THREADS, smem, st>>>((const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)gate, gate_stride,
-                                                          (const __nv_bfloat16*)kc, (const __nv_bfloat16*)vc, pos_ids, sink, scale, softcap,
-                                                          Tn, H, G, dim, vdim, window, chunk, ring, (__nv_bfloat16*)y);
+  softmax_attn_mma_kernel<D, MAPS><<<grid, TM_THREADS, smem, st>>>(
+      (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)gate, gate_stride, (const __nv_bfloat16*)kc, (const __nv_bfloat16*)vc,
+      pos_ids, sink, scale, softcap, Tn, H, G, dim, vdim, window, chunk, ring, dm.lambda, dm.post, dm.eps, (__nv_bfloat16*)y);
   LL_LAUNCH_OK("softmax_attn_mma_kernel");
   return LL_OK;
 }
@@ -544,24 +625,25 @@ using namespace llb;
 
 extern "C" {
 
-int ll_qk_rotary_append(const void* q, int q_stride, const void* k, int k_stride, const void* v, int v_stride, int dtype,
-                        const float* q_norm, const float* k_norm, float eps, const float* freq, int rot_dims,
-                        const int32_t* pos_ids, void* q_out, void* kc, void* vc, int B, int T, int H, int G, int dim, int vdim, int ring,
-                        ll_stream stream) {
-  LL_CHECK_ARG(q && q_out && pos_ids && B >= 0 && T >= 0 && H > 0 && dim > 0, "bad qk_rotary_append arguments");
+int ll_qk_rotary_append_maps(const void* q, int q_stride, const void* k, int k_stride, const void* v, int v_stride, int dtype,
+                             const float* q_norm, const float* k_norm, float eps, const float* freq, int rot_dims,
+                             const int32_t* pos_ids, void* q_out, void* kc, void* vc, int B, int T, int H, int G, int dim, int vdim,
+                             int ring, int maps, ll_stream stream) {
+  LL_CHECK_ARG((q || k) && (!q || q_out) && pos_ids && B >= 0 && T >= 0 && H > 0 && dim > 0 && maps >= 1,
+               "bad qk_rotary_append arguments");
   LL_CHECK_ARG(rot_dims >= 0 && rot_dims <= dim && rot_dims % 2 == 0 && (rot_dims == 0 || freq), "qk_rotary_append: bad rotation");
   LL_CHECK_ARG(!k || (kc && vc && G > 0 && vdim > 0 && ring > 0), "qk_rotary_append: keys need their ring");
-  LL_CHECK_ARG(!k || v || vdim == dim, "qk_rotary_append: values taken from the keys have the keys' size");
+  LL_CHECK_ARG(!k || v || (vdim == dim && maps == 1), "qk_rotary_append: values taken from the keys have the keys' size");
   if (B == 0 || T == 0) return LL_OK;
   cudaStream_t st = (cudaStream_t)stream;
   if (dtype == LL_F32)
     qk_rotary_append_kernel<float><<<B * T, QP_THREADS, 0, st>>>((const float*)q, q_stride, (const float*)k, k_stride, (const float*)v,
                                                                 v_stride, q_norm, k_norm, eps, freq, rot_dims, pos_ids, (float*)q_out,
-                                                                (float*)kc, (float*)vc, T, H, G, dim, vdim, ring);
+                                                                (float*)kc, (float*)vc, T, H, G, dim, vdim, ring, maps);
   else if (dtype == LL_BF16)
     qk_rotary_append_kernel<__nv_bfloat16><<<B * T, QP_THREADS, 0, st>>>(
         (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)k, k_stride, (const __nv_bfloat16*)v, v_stride, q_norm, k_norm, eps,
-        freq, rot_dims, pos_ids, (__nv_bfloat16*)q_out, (__nv_bfloat16*)kc, (__nv_bfloat16*)vc, T, H, G, dim, vdim, ring);
+        freq, rot_dims, pos_ids, (__nv_bfloat16*)q_out, (__nv_bfloat16*)kc, (__nv_bfloat16*)vc, T, H, G, dim, vdim, ring, maps);
   else {
     set_error("qk_rotary_append: unsupported dtype %d", dtype);
     return LL_ERR_UNSUPPORTED;
@@ -570,17 +652,31 @@ int ll_qk_rotary_append(const void* q, int q_stride, const void* k, int k_stride
   return LL_OK;
 }
 
+int ll_qk_rotary_append(const void* q, int q_stride, const void* k, int k_stride, const void* v, int v_stride, int dtype,
+                        const float* q_norm, const float* k_norm, float eps, const float* freq, int rot_dims,
+                        const int32_t* pos_ids, void* q_out, void* kc, void* vc, int B, int T, int H, int G, int dim, int vdim, int ring,
+                        ll_stream stream) {
+  LL_CHECK_ARG(q, "bad qk_rotary_append arguments");
+  return ll_qk_rotary_append_maps(q, q_stride, k, k_stride, v, v_stride, dtype, q_norm, k_norm, eps, freq, rot_dims, pos_ids, q_out, kc,
+                                  vc, B, T, H, G, dim, vdim, ring, 1, stream);
+}
+
+int ll_softmax_attn_tensor_form(int dtype, int T, int dim, int vdim, int q_stride, int gate_stride, int splits) {
+  return tm_supported(dtype, T, dim, vdim, q_stride, gate_stride, splits) ? 1 : 0;
+}
+
 size_t ll_softmax_attn_scratch_bytes(int M, int H, int vdim, int splits) {
-  if (splits <= 1) return 16;
+  if (splits < 1) return 16;
   return (size_t)M * H * splits * (2 + (size_t)vdim) * sizeof(float);
 }
 
-int ll_softmax_attn(const void* q, int q_stride, const void* gate, int gate_stride, const void* kc, const void* vc, int dtype,
-                    const int32_t* pos_ids, const float* sink, float scale, float softcap, int B, int T, int H, int G, int dim,
-                    int vdim, int window, int chunk, int ring, int splits, int form, float* scratch, void* y, ll_stream stream) {
+int ll_softmax_attn_maps(const void* q, int q_stride, const void* gate, int gate_stride, const void* kc, const void* vc, int dtype,
+                         const int32_t* pos_ids, const float* sink, float scale, float softcap, int B, int T, int H, int G, int dim,
+                         int vdim, int window, int chunk, int ring, int splits, int form, int maps, float diff_lambda, float diff_post,
+                         float eps, float* scratch, void* y, ll_stream stream) {
   LL_CHECK_ARG(q && kc && vc && pos_ids && y, "softmax_attn: null pointer");
   LL_CHECK_ARG(B >= 0 && T >= 0 && H > 0 && G > 0 && H % G == 0 && dim > 0 && vdim > 0 && ring > 0 && window >= 0 && chunk >= 0 &&
-                   splits >= 1 && (splits == 1 || scratch),
+                   splits >= 1 && (maps == 1 || maps == 2),
                "bad softmax_attn arguments");
   if (dim > 256 || vdim > 256) {
     set_error("softmax_attn: heads of %d / %d dimensions (up to 256)", dim, vdim);
@@ -588,23 +684,36 @@ int ll_softmax_attn(const void* q, int q_stride, const void* gate, int gate_stri
   }
   if (B == 0 || T == 0) return LL_OK;
   cudaStream_t st = (cudaStream_t)stream;
+  const DiffMaps dm{maps, diff_lambda, diff_post, eps};
   if (form == 0 && tm_supported(dtype, T, dim, vdim, q_stride, gate ? gate_stride : 0, splits)) {
     const int d = dim > vdim ? dim : vdim;
 #define LL_TM(DD)                                                                                                                   \
-  if (d <= DD)                                                                                                                      \
-    return tm_launch<DD>(q, q_stride, gate, gate_stride, kc, vc, pos_ids, sink, scale, softcap, B, T, H, G, dim, vdim, window, chunk, ring, \
-                         y, st);
+  if (d <= DD) {                                                                                                                    \
+    if (maps == 1)                                                                                                                  \
+      return tm_launch<DD, 1>(q, q_stride, gate, gate_stride, kc, vc, pos_ids, sink, scale, softcap, B, T, H, G, dim, vdim, window,  \
+                              chunk, ring, dm, y, st);                                                                              \
+    return tm_launch<DD, 2>(q, q_stride, gate, gate_stride, kc, vc, pos_ids, sink, scale, softcap, B, T, H, G, dim, vdim, window,    \
+                            chunk, ring, dm, y, st);                                                                                \
+  }
     LL_TM(32) LL_TM(64) LL_TM(96) LL_TM(128)
 #undef LL_TM
   }
+  LL_CHECK_ARG(scratch || (splits == 1 && maps == 1), "softmax_attn: split key ranges and several maps meet in scratch memory");
   if (dtype == LL_F32)
     return sa_dispatch<float>(q, q_stride, gate, gate_stride, kc, vc, pos_ids, sink, scale, softcap, B, T, H, G, dim, vdim, window, chunk,
-                              ring, splits, scratch, y, st);
+                              ring, splits, dm, scratch, y, st);
   if (dtype == LL_BF16)
     return sa_dispatch<__nv_bfloat16>(q, q_stride, gate, gate_stride, kc, vc, pos_ids, sink, scale, softcap, B, T, H, G, dim, vdim, window,
-                                      chunk, ring, splits, scratch, y, st);
+                                      chunk, ring, splits, dm, scratch, y, st);
   set_error("softmax_attn: unsupported dtype %d", dtype);
   return LL_ERR_UNSUPPORTED;
+}
+
+int ll_softmax_attn(const void* q, int q_stride, const void* gate, int gate_stride, const void* kc, const void* vc, int dtype,
+                    const int32_t* pos_ids, const float* sink, float scale, float softcap, int B, int T, int H, int G, int dim,
+                    int vdim, int window, int chunk, int ring, int splits, int form, float* scratch, void* y, ll_stream stream) {
+  return ll_softmax_attn_maps(q, q_stride, gate, gate_stride, kc, vc, dtype, pos_ids, sink, scale, softcap, B, T, H, G, dim, vdim,
+                              window, chunk, ring, splits, form, 1, 0.f, 1.f, 0.f, scratch, y, stream);
 }
 
 }  // extern "C"

@@ -134,6 +134,15 @@ EXPORTS = {
     "ll_softmax_attn_scratch_bytes": ([i32, i32, i32, i32], sz_t),
     "ll_softmax_attn": ([vp, i32, vp, i32, vp, vp, i32, vp, vp, C.c_float, C.c_float, i32, i32, i32, i32, i32, i32, i32, i32, i32,
                          i32, i32, vp, vp, vp], C.c_int),
+    "ll_qk_rotary_append_maps": ([vp, i32, vp, i32, vp, i32, i32, vp, vp, C.c_float, vp, i32, vp, vp, vp, vp, i32, i32, i32, i32, i32,
+                                  i32, i32, i32, vp], C.c_int),
+    "ll_softmax_attn_tensor_form": ([i32, i32, i32, i32, i32, i32, i32], C.c_int),
+    "ll_softmax_attn_maps": ([vp, i32, vp, i32, vp, vp, i32, vp, vp, C.c_float, C.c_float, i32, i32, i32, i32, i32, i32, i32, i32,
+                              i32, i32, i32, i32, C.c_float, C.c_float, C.c_float, vp, vp, vp], C.c_int),
+    "ll_hyper_mix_norm": ([vp, i64, i64, vp, vp, vp, C.c_float, vp, vp, vp, vp, C.c_float, vp, i32, vp, i32, i32, i32, i32, vp], C.c_int),
+    "ll_row_norm": ([vp, i32, vp, C.c_float, vp, i32, i32, i32, i32, vp], C.c_int),
+    "ll_sigmoid_gate_mul": ([vp, i32, vp, i32, vp, i32, i32, i32, i32, vp], C.c_int),
+    "ll_tanh_cap": ([vp, C.c_float, sz_t, vp], C.c_int),
     "ll_ssm_gates": ([vp, i32, i32, vp, vp, vp, vp, i32, i32, vp], C.c_int),
     "ll_channel_decay": ([vp, i32, i32, vp, C.c_float, vp, i32, i32, vp], C.c_int),
     "ll_sink_ring_append": ([vp, i32, vp, i32, i32, vp, vp, vp, i32, i32, i32, i32, i32, i32, vp], C.c_int),
@@ -143,7 +152,7 @@ EXPORTS = {
 }
 _fn = {name: _proto(name, a, r) for name, (a, r) in EXPORTS.items()}
 
-ABI_VERSION = 14
+ABI_VERSION = 15
 if _fn["ll_abi_version"]() != ABI_VERSION:
     raise ImportError("libllb200.so ABI version mismatch; rebuild with lit-llama-ja_b200/build.py")
 

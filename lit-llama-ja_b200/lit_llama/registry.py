@@ -39,6 +39,10 @@ def _builtin() -> None:
         from .tebodra import ARCHITECTURE, Tebodra
 
         register_architecture(ARCHITECTURE, Tebodra.from_dir)
+    if "Bumulix" not in _FROM_DIR:
+        from .bumulix import ARCHITECTURE, Bumulix
+
+        register_architecture(ARCHITECTURE, Bumulix.from_dir)
 
 
 def load_model_dir(path, dtype: torch.dtype = torch.bfloat16, device="cuda"):

@@ -10,10 +10,17 @@ sigmoid gate on the heads' outputs, with the variations models differ in as para
     w = exp(s) / (sum_visible exp(s) [+ exp(sink_h)])         the sink is a learned number per head without key or value
     out = W_o( concat_h( sum_j w v_g(j) ) * sigmoid(W_g h) )
 
+With ``maps`` = 2 every head carries two score maps (differential attention): the q and k projections hold ``[map 0 | map 1]``
+per head, both maps attend over the same values, and the head's output is
+
+    o = a_0 - lam * a_1,   lam = exp(lq1 . lk1) - exp(lq2 . lk2) + diff,       o <- o / sqrt(mean(o^2) + eps) * (1 - diff)
+
+(``lq1`` ... ``lk2`` learned vectors of the layer, ``diff`` a constant of the spec).  ``gate`` False: no sigmoid gate.
+
 A layer with ``kv_from`` set has no key / value tensors: it appends nothing and reads the ring of the layer it names
 (whose keys are stored after norm and rotation), with its own queries, mask, sink and gate.
 
-Cache: ``[B, R, G * dim]`` keys and ``[B, R, G * vdim]`` values, position j at slot ``j % R`` (csrc/rotary_attn.cu).
+Cache: ``[B, R, G * maps * dim]`` keys and ``[B, R, G * vdim]`` values, position j at slot ``j % R`` (csrc/rotary_attn.cu).
 """
 from __future__ import annotations
 
@@ -51,12 +58,19 @@ class SoftmaxAttentionSpec:
     conv_taps: int = 0                   # 0: no short convolution on q and k
     own_values: bool = True              # False: the values are the un-rotated keys
     kv_from: Optional[int] = None        # index of the layer whose ring this layer reads
+    maps: int = 1                        # score maps per head; 2: the difference of two softmax maps with a unit norm per head
+    diff: float = 0.0                    # the constant of the two-map combination
+    gate: bool = True                    # sigmoid(W_g h) on the heads' outputs
 
     def __post_init__(self):
         if self.heads % self.kv_heads:
             raise ValueError(f"{self.heads} query heads over {self.kv_heads} key/value heads")
         if not self.own_values and self.vdim != self.dim:
             raise ValueError("values taken from the keys have the keys' size")
+        if self.maps not in (1, 2):
+            raise ValueError(f"{self.maps} score maps per head (1 or 2)")
+        if self.maps > 1 and not self.own_values:
+            raise ValueError("values taken from the keys need one score map per head")
         if self.rotary.dims > self.dim:
             raise ValueError(f"{self.rotary.dims} rotated dimensions in heads of {self.dim}")
 
@@ -73,9 +87,10 @@ class SoftmaxAttention(nn.Module):
         s = self.spec = spec
         kw = dict(dtype=dtype, device=device)
         f32 = dict(dtype=torch.float32, device=device)
-        hd, gd, gv, hv = s.heads * s.dim, s.kv_heads * s.dim, s.kv_heads * s.vdim, s.heads * s.vdim
+        hd, gd, gv, hv = s.heads * s.maps * s.dim, s.kv_heads * s.maps * s.dim, s.kv_heads * s.vdim, s.heads * s.vdim
         self.owner = s.kv_from is None
-        names, at = [("q", hd)] + ([("k", gd)] if self.owner else []) + ([("v", gv)] if self.owner and s.own_values else []) + [("g", hv)], 0
+        names, at = [("q", hd)] + ([("k", gd)] if self.owner else []) + ([("v", gv)] if self.owner and s.own_values else []) \
+            + ([("g", hv)] if s.gate else []), 0
         self.cols = {}
         for name, n in names:
             self.cols[name] = at
@@ -86,8 +101,11 @@ class SoftmaxAttention(nn.Module):
         self.conv = ShortConv(self.conv_channels, s.conv_taps, False, device) if s.conv_taps > 0 else None
         self.q_norm = nn.Parameter(torch.ones(hd, **f32), requires_grad=False) if s.qk_norm else None
         self.k_norm = nn.Parameter(torch.ones(gd, **f32), requires_grad=False) if s.qk_norm and self.owner else None
-        self.sink = nn.Parameter(torch.zeros(s.heads, **f32), requires_grad=False) if s.sink else None
+        self.sink = nn.Parameter(torch.zeros(s.heads * s.maps, **f32), requires_grad=False) if s.sink else None
         self.register_buffer("freq", s.rotary.frequencies(device), persistent=False)
+        self.diff_lambda = 0.0                         # lam of the two-map combination, formed at load time
+        # queries that are neither filtered, normed nor turned are read where the input projection left them
+        self.plain_q = self.conv is None and not s.qk_norm and s.rotary.dims == 0
         self.w_o = nn.Parameter(torch.zeros((s.width, hv), **kw), requires_grad=False)
 
     def state_shapes(self, B: int) -> List[Tuple[int, ...]]:
@@ -95,7 +113,7 @@ class SoftmaxAttention(nn.Module):
 
     def cache_shapes(self, B: int, ring: int) -> List[Tuple[int, ...]]:
         s = self.spec
-        return [(B, ring, s.kv_heads * s.dim), (B, ring, s.kv_heads * s.vdim)] if self.owner else []
+        return [(B, ring, s.kv_heads * s.maps * s.dim), (B, ring, s.kv_heads * s.vdim)] if self.owner else []
 
     def load(self, get) -> None:
         """``get(suffix)`` returns the tensor '<layer>.mix.<suffix>'."""
@@ -110,6 +128,9 @@ class SoftmaxAttention(nn.Module):
             self.k_norm.copy_(get("k.norm").float())
         if self.sink is not None:
             self.sink.copy_(get("sink").float())
+        if s.maps == 2:
+            l = [get(n).double() for n in ("lq1", "lk1", "lq2", "lk2")]
+            self.diff_lambda = float(torch.exp((l[0] * l[1]).sum()) - torch.exp((l[2] * l[3]).sum()) + s.diff)
         self.w_o.copy_(get("o"))
 
     def forward(self, u: torch.Tensor, B: int, T: int, pos_ids: torch.Tensor, caches, conv_state=None, splits: int = 1,
@@ -127,7 +148,7 @@ class SoftmaxAttention(nn.Module):
         dtc = N.dtype_code(proj.dtype)
         ring = kc.shape[1]
         st = N.stream()
-        hd = s.heads * s.dim
+        hd = s.heads * s.maps * s.dim
         if self.conv is not None:
             src = self.conv(proj, 0, conv_state, pos_ids, B, T, proj.dtype)
             q_at, k_at = N.ptr(src), N.ptr_at(src, hd)
@@ -135,16 +156,23 @@ class SoftmaxAttention(nn.Module):
             src = proj
             q_at, k_at = N.ptr_at(proj, c["q"]), (N.ptr_at(proj, c["k"]) if self.owner else None)
         v_at = N.ptr_at(proj, c["v"]) if "v" in c else None
-        q = torch.empty((M, hd), dtype=proj.dtype, device=proj.device)
-        N.call("ll_qk_rotary_append", q_at, src.stride(0), k_at if self.owner else None, src.stride(0), v_at, proj.stride(0), dtc,
-               N.ptr(self.q_norm), N.ptr(self.k_norm), float(s.eps), N.ptr(self.freq), s.rotary.dims, N.ptr(pos_ids), N.ptr(q),
-               N.ptr(kc), N.ptr(vc), B, T, s.heads, s.kv_heads, s.dim, s.vdim, ring, st)
+        if self.plain_q:
+            q, q_ptr, q_stride = None, q_at, src.stride(0)
+        else:
+            q = torch.empty((M, hd), dtype=proj.dtype, device=proj.device)
+            q_ptr, q_stride = N.ptr(q), hd
+        if self.owner or not self.plain_q:
+            N.call("ll_qk_rotary_append_maps", None if self.plain_q else q_at, src.stride(0), k_at if self.owner else None, src.stride(0),
+                   v_at, proj.stride(0), dtc, N.ptr(self.q_norm), N.ptr(self.k_norm), float(s.eps), N.ptr(self.freq), s.rotary.dims,
+                   N.ptr(pos_ids), N.ptr(q), N.ptr(kc), N.ptr(vc), B, T, s.heads, s.kv_heads, s.dim, s.vdim, ring, s.maps, st)
+        gate_at, gate_stride = (N.ptr_at(proj, c["g"]), proj.stride(0)) if s.gate else (None, 0)
         scratch = None
-        if splits > 1:
-            scratch = torch.empty(N.call_ret("ll_softmax_attn_scratch_bytes", M, s.heads, s.vdim, splits) // 4, dtype=torch.float32,
-                                  device=proj.device)
+        if splits > 1 or (s.maps > 1 and (form != 0 or not N.call_ret("ll_softmax_attn_tensor_form", dtc, T, s.dim, s.vdim, q_stride,
+                                                                       gate_stride, splits))):
+            scratch = torch.empty(N.call_ret("ll_softmax_attn_scratch_bytes", M, s.heads * s.maps, s.vdim, splits) // 4,
+                                  dtype=torch.float32, device=proj.device)
         y = torch.empty((M, s.heads * s.vdim), dtype=proj.dtype, device=proj.device)
-        N.call("ll_softmax_attn", N.ptr(q), hd, N.ptr_at(proj, c["g"]), proj.stride(0), N.ptr(kc), N.ptr(vc), dtc, N.ptr(pos_ids),
+        N.call("ll_softmax_attn_maps", q_ptr, q_stride, gate_at, gate_stride, N.ptr(kc), N.ptr(vc), dtc, N.ptr(pos_ids),
                N.ptr(self.sink), float(s.scale), float(s.softcap), B, T, s.heads, s.kv_heads, s.dim, s.vdim, s.window or 0, s.chunk or 0,
-               ring, splits, form, N.ptr(scratch), N.ptr(y), st)
+               ring, splits, form, s.maps, float(self.diff_lambda), float(1.0 - s.diff), float(s.eps), N.ptr(scratch), N.ptr(y), st)
         return y

@@ -145,3 +145,17 @@ def add_norm_pair(x, branches, w1, w2, eps, out1, out2, act_dtype) -> None:
     N.call("ll_add_norm_pair", N.ptr(x), N.ptr(b[0][0]), float(b[0][1]), N.ptr(b[1][0]), float(b[1][1]), N.ptr(b[2][0]), float(b[2][1]),
            N.ptr(w1), N.ptr(w2), float(eps), N.ptr(out1), 1 if (out1 is not None and out1.dtype == torch.float32) else 0, N.ptr(out2),
            N.dtype_code(act_dtype), x.shape[0], x.shape[1], N.stream())
+
+
+def hyper_mix_norm(src, X, pending, r, w_in, w, eps, h, total, act_dtype) -> None:
+    """One launch between two sublayers of a model whose stream is kept as copies ``X [rows, S, width]`` (fp32, updated in
+    place): the result of the sublayer before (``pending`` = (y, per-channel scale or None, its HyperConnection); None: there
+    is none) goes into all copies, ``X'[t] = sum_s mix[s, t] X[s] + r * out[t] * scale * y``; then ``h = rmsnorm(sum_t
+    w_in[t] X'[t]) * w`` (``w_in`` None: the plain sum) and, if asked for, ``total`` = the plain sum of the copies.  ``src``
+    is ``X``, or the embedding output ``[rows, width]`` that every copy starts as."""
+    M, S, E = X.shape
+    y, ls, hc = pending if pending is not None else (None, None, None)
+    spread = src is not X
+    N.call("ll_hyper_mix_norm", N.ptr(src), E if spread else S * E, 0 if spread else E, N.ptr(X), N.ptr(y), N.ptr(ls), float(r),
+           N.ptr(hc.mix) if hc is not None else None, N.ptr(hc.w_out) if hc is not None else None, N.ptr(w_in), N.ptr(w), float(eps),
+           N.ptr(h), 1 if (h is not None and h.dtype == torch.float32) else 0, N.ptr(total), N.dtype_code(act_dtype), M, S, E, N.stream())

@@ -121,7 +121,7 @@ def latent_attention(h, W, m, eps, positions=None):
     T = h.shape[0]
     H, d, r, dv, kr = int(m["heads"]), int(m["dim"]), int(m["rot_dim"]), int(m["vdim"]), int(m["kv_rank"])
     positions = np.arange(T) if positions is None else positions
-    rot = dict(m["rot"], dims=r) if m.get("rot") else {"dims": 0, "base": 1.0}
+    rot = dict(m["rot"], dims=m["rot"].get("dims", r)) if m.get("rot") else {"dims": 0, "base": 1.0}
     cq = unit_rms(h @ W["dq"].T, eps) * W["dq.norm"]
     q = (cq @ W["uq"].T).reshape(T, H, d + r)
     kv = h @ W["dkv"].T
