@@ -116,7 +116,8 @@ class BumulixConfig:
                     window=int(mask["size"]) if mask.get("size") is not None else None, maps=maps, diff=float(m.get("diff", 0.0)),
                     gate=False)
             elif kind == "latent_attention":
-                heads, dim, rot_dim = int(m["heads"]), int(m["dim"]), int(m.get("rot_dim") or 0)
+                dim, rot_dim = int(m["dim"]), int(m.get("rot_dim") or 0)
+                heads = pick(m.get("heads"), p + "uk", 0, dim)
                 rot = m.get("rot") if rot_dim else None
                 rotary = RotarySpec.from_dict(rot, rot_dim) if rot else RotarySpec(0)
                 q_rank = m.get("q_rank")
