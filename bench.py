@@ -49,9 +49,9 @@ def parse():
     ap.add_argument("--steps", type=int, default=3)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--family", default=None, choices=[None, "lepalorn", "bededra", "tebodra"],
+    ap.add_argument("--family", default=None, choices=[None, "lepalorn", "bededra", "tebodra", "bumulix"],
                     help="instead of the headline workload: prefill / decode throughput and kernel rooflines of this model family "
-                         "beside its closest relative at equal size (lepalorn beside LLaMA, bededra beside lepalorn, tebodra beside bededra; 1 GPU; one JSON "
+                         "beside its closest relative at equal size (lepalorn beside LLaMA, bededra beside lepalorn, tebodra beside bededra, bumulix beside tebodra; 1 GPU; one JSON "
                          "line of its own)")
     ap.add_argument("--size", default=None, help="with --family: one of the family's sizes (default: all)")
     return ap.parse_args()

@@ -538,6 +538,163 @@ def run_tebodra(args):
     return 0
 
 
+# two-map attention: maps of dim (together Tebodra's head size), values of 2 * dim; latent attention as in the Lepalorn sizes
+BUMULIX_SIZES = {
+    "w1024": dict(width=1024, layers=4, heads=8, kv=2, dim=32, vdim=64, window=512, l_heads=8, nope=64, rot=32, v=64, kv_rank=256,
+                  q_rank=384, ff=4096, streams=2),
+    "w2048": dict(width=2048, layers=4, heads=16, kv=4, dim=64, vdim=128, window=1024, l_heads=16, nope=128, rot=64, v=128, kv_rank=512,
+                  q_rank=768, ff=8192, streams=2),
+    "w4096": dict(width=4096, layers=2, heads=32, kv=8, dim=64, vdim=128, window=2048, l_heads=32, nope=128, rot=64, v=128, kv_rank=512,
+                  q_rank=1536, ff=16384, streams=2),
+}
+
+
+def bumulix_model(s, device, dtype=torch.bfloat16):
+    from lit_llama.bumulix import Bumulix, BumulixConfig
+
+    ff = {"kind": "dense", "ff": s["ff"]}
+    window = {"type": "attention", "mlp": ff, "mixer": {
+        "heads": s["heads"], "kv_heads": s["kv"], "dim": s["dim"], "vdim": s["vdim"], "diff": 0.5, "scale": s["dim"] ** -0.5,
+        "mask": {"size": s["window"]}}}
+    lat = {"type": "latent_attention", "mlp": ff, "mixer": {
+        "heads": s["l_heads"], "dim": s["nope"], "rot_dim": s["rot"], "vdim": s["v"], "kv_rank": s["kv_rank"], "q_rank": s["q_rank"],
+        "scale": (s["nope"] + s["rot"]) ** -0.5,
+        "rot": {"base": 10000.0, "dims": s["rot"], "scaling": {"factor": 8.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}}
+    cycle = [window, lat, dict(window, weights_of=0), dict(lat, weights_of=1)] if s["layers"] >= 4 else [window, lat]
+    cfg = {"vocab": VOCAB, "width": s["width"], "norm": {"eps": 1e-5}, "residual_mult": 0.5, "streams": s["streams"], "logit_softcap": 30.0,
+           "layers": [cycle[i % len(cycle)] for i in range(s["layers"])]}
+    m = Bumulix(BumulixConfig.from_dict(cfg), dtype=dtype, device=device)
+    g = torch.Generator(device=device).manual_seed(0)
+    for n, p in m.named_parameters():
+        if p.dim() >= 2 and ".hc" not in n:
+            p.copy_((torch.randn(p.shape, generator=g, device=device) / math.sqrt(p.shape[-1])).to(p.dtype))
+    for b in m.blocks:
+        if b.kind == "attention":
+            b.mix.diff_lambda = 0.6
+    return m.eval()
+
+
+def bumulix_kernel_table(s, model, device, timer, prompt_len):
+    """The mixers' kernels alone, one layer of each kind, and the stream update.  Roofline time = max(flops / tensor peak,
+    bytes / copy bandwidth), flops and bytes counted for the mechanism (one sweep over the visible keys per score map; every
+    copy of the stream read and written once), not for what the kernel happens to do."""
+    from torch.nn import functional as F
+
+    from lit_llama import _native as N
+    from lit_llama.stepping import hyper_mix_norm
+
+    hbm, tflops, which = peaks()
+    bf = torch.bfloat16
+    rows = []
+
+    def add(name, t, flops, nbytes):
+        roof = max(flops / tflops, nbytes / hbm)
+        rows.append(dict(kernel=name, us=round(t * 1e6, 1), roofline_us=round(roof * 1e6, 2), fraction=round(roof / t, 4)))
+
+    E, S = s["width"], s["streams"]
+    first = {}
+    for i, (l, b) in enumerate(zip(model.config.layers, model._block_of)):
+        first.setdefault(l.kind, (i, b))
+    sms = torch.cuda.get_device_properties(device).multi_processor_count
+    for T, tag in ((prompt_len, "prefill"), (1, "decode")):
+        pos0 = 0 if T > 1 else prompt_len
+        pos_ids = torch.arange(pos0, pos0 + T, dtype=torch.int32, device=device)
+        model.reset_cache()
+        model._begin(1, prompt_len + 64, True)
+        for t in model.kv_caches:
+            t.normal_()
+        x = torch.randn((T, E), device=device, dtype=bf)
+        # two score maps over a window
+        i, blk = first["attention"]
+        att, spec = blk.mix, blk.mix.spec
+        at = model._cache_at[i]
+        caches = model.kv_caches[at:at + 2]
+        proj = F.linear(x, att.w_in)
+        H, G, D, V, W = spec.heads, spec.kv_heads, spec.dim, spec.vdim, spec.window
+        span = min(W, caches[0].shape[1])
+        splits = 1 if T > 1 else max(1, min(64, (2 * sms) // max(1, (H * 2 + 3) // 4), (span + 31) // 32))
+        keys = sum(min(p + 1, W) for p in range(pos0, pos0 + T))
+        rows_read = min(pos0 + T, W + T - 1)
+        add(f"two-map attention {tag} (append + attention + difference + unit norm)",
+            timer(lambda: att.attend(proj, 1, T, pos_ids, caches, None, splits), graph=True),
+            2.0 * keys * H * 2 * (D + V), 2.0 * (rows_read * G * (2 * D + V) + T * (H * 2 * D + G * (2 * D + V) + H * V)))
+        # latent attention over the whole past
+        i, blk = first["latent_attention"]
+        lat, ls = blk.mix, blk.mix.spec
+        cache = model.kv_caches[model._cache_at[i]]
+        rope = model._rope[next(iter(model._rope))]
+        lsplits = 1 if T > 1 else max(1, min(16, (2 * sms) // max(1, (ls.heads + 31) // 32), (cache.shape[1] + 63) // 64))
+        lkeys = sum(p + 1 for p in range(pos0, pos0 + T))
+        proj_l = F.linear(x, lat.w_in)
+        cq = torch.empty((T, ls.q_rank), dtype=bf, device=device)
+        q = F.linear(cq, lat.w_uq)
+        q_lat = torch.randn((ls.heads, T, ls.kv_rank), dtype=bf, device=device)
+        o_lat = torch.empty_like(q_lat)
+        o = torch.randn((T, ls.heads * ls.v_dim), dtype=bf, device=device)
+        scratch = torch.empty(N.call_ret("ll_latent_attn_scratch_bytes", T, ls.heads, ls.kv_rank, lsplits) // 4 + 4, device=device)
+        dt = N.dtype_code(bf)
+
+        def latent_kernels():
+            st = N.stream()
+            N.call("ll_latent_kv_append", N.ptr(proj_l), dt, proj_l.shape[1], lat.kv_col0, N.ptr(lat.kv_norm), 1e-5, N.ptr(rope),
+                   N.ptr(pos_ids), N.ptr(cache), 1, T, ls.kv_rank, ls.rot_dim, ls.rot_dims, cache.shape[1], st)
+            N.call("ll_row_norm", N.ptr(proj_l), proj_l.shape[1], N.ptr(lat.q_norm), 1e-5, N.ptr(cq), ls.q_rank, dt, T, ls.q_rank, st)
+            N.call("ll_latent_attn", N.ptr(q_lat), T * ls.kv_rank, ls.kv_rank, N.ptr(q), q.shape[1], ls.nope_dim, ls.q_head, -1,
+                   N.ptr(rope), N.ptr(pos_ids), N.ptr(cache), N.ptr(o_lat), T * ls.kv_rank, ls.kv_rank, dt, 1, T, ls.heads, ls.kv_rank,
+                   ls.rot_dim, ls.rot_dims, cache.shape[1], 0, float(ls.scale), lsplits, N.ptr(scratch), st)
+            N.call("ll_sigmoid_gate_mul", N.ptr(o), o.shape[1], N.ptr_at(proj_l, lat.gate_col0), proj_l.shape[1], N.ptr(o), o.shape[1], dt,
+                   T, ls.heads * ls.v_dim, st)
+
+        add(f"latent attention {tag} (latent norms + append + attention in latent space + element-wise gate)",
+            timer(latent_kernels, graph=True), 2.0 * lkeys * ls.heads * (2 * ls.kv_rank + ls.rot_dim),
+            2.0 * ((pos0 + T) * ls.row + T * ls.heads * (2 * ls.kv_rank + ls.rot_dim + 2 * ls.v_dim)))
+        # the stream: one sublayer's result into all copies, the next sublayer's input out
+        X = torch.randn((T, S, E), device=device)
+        y = torch.randn((T, E), device=device, dtype=bf)
+        h = torch.empty((T, E), device=device, dtype=bf)
+        add(f"stream copies: write + read + norm {tag}",
+            timer(lambda: hyper_mix_norm(X, X, (y, blk.ls1, blk.hc1), 0.5, blk.hc2.w_in, blk.norm2, 1e-5, h, None, bf), graph=True), 0.0,
+            T * E * (8 * S + 2 + 2))
+        hh = torch.randn((T, s["ff"]), device=device, dtype=bf)
+        add(f"gelu (tanh form) {tag}", timer(lambda: N.call("ll_gelu", N.ptr(hh), dt, 1, hh.numel(), N.stream()), graph=True), 0.0,
+            T * s["ff"] * 4)
+    return rows, which
+
+
+def run_bumulix(args):
+    import sys
+
+    sys.path.insert(0, str(ROOT))
+    from __graft_entry__ import build
+
+    build()
+    device = torch.device("cuda", 0)
+    torch.cuda.set_device(device)
+    timer = Timer(device)
+    prompt_len = 2048
+    out = {"family": "bumulix", "beside": "tebodra", "dtype": "bf16", "data": "synthetic (random weights)", "prompt_len": prompt_len,
+           "batch": 1, "l2": "256 MB written between timed iterations", "sizes": {}}
+    names = [n for n in BUMULIX_SIZES if not getattr(args, "size", None) or n == args.size]
+    for name in names:
+        s = BUMULIX_SIZES[name]
+        with torch.no_grad():
+            m = bumulix_model(s, device)
+            pre, dec = end_to_end(m, timer, prompt_len, device, prompt_len + 64)
+            rows, which = bumulix_kernel_table(s, m, device, timer, prompt_len)
+            del m
+            torch.cuda.empty_cache()
+            teb = tebodra_model(TEBODRA_SIZES[name], device)
+            tpre, tdec = end_to_end(teb, timer, prompt_len, device, prompt_len + 64)
+            trows, _ = tebodra_kernel_table(TEBODRA_SIZES[name], teb, device, timer, prompt_len)
+            del teb
+            torch.cuda.empty_cache()
+        out["sizes"][name] = {"config": s, "bumulix": {"prefill_tokens_per_s": round(pre), "decode_tokens_per_s": round(dec, 1)},
+                              "tebodra_same_width": {"prefill_tokens_per_s": round(tpre), "decode_tokens_per_s": round(tdec, 1)},
+                              "kernels": rows, "tebodra_kernels": trows, "roofline": f"of {which}"}
+    print(json.dumps(out))
+    return 0
+
+
 def run(args):
     import sys
 
@@ -545,6 +702,8 @@ def run(args):
         return run_bededra(args)
     if args.family == "tebodra":
         return run_tebodra(args)
+    if args.family == "bumulix":
+        return run_bumulix(args)
     sys.path.insert(0, str(ROOT))
     from __graft_entry__ import build
 

@@ -262,42 +262,59 @@ __global__ void __launch_bounds__(SA_WARPS * 32) softmax_attn_kernel(
     }
 }
 
-// Merge of the key ranges of one (query, head), in order; a warp per pair, a lane per value dimension.  With two maps per
-// head the warp merges both and combines them: o = a_0 - lambda * a_1, o / sqrt(mean(o^2) + eps) * post.
+// Merge of the key ranges of one (query, head), in order; a warp per pair, a lane per value dimension.  The weight of every
+// range (e^(m_s - m) / denominator) is formed once, a lane per range, and kept in shared memory, so that the sums over the
+// ranges are loads that do not wait for one another.  With two maps per head the warp merges both and combines them:
+// o = a_0 - lambda * a_1, o / sqrt(mean(o^2) + eps) * post.
+constexpr int SA_MAX_SPLITS = 64;
 template <typename T>
 __global__ void softmax_attn_merge_kernel(const float* __restrict__ part_ml, const float* __restrict__ part_acc,
                                           const T* __restrict__ gate, int gate_stride, const float* __restrict__ sink, int H, int vdim,
                                           int splits, int maps, float lambda, float post, float eps, int pairs, T* __restrict__ y) {
-  const int pair = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);      // (query, head)
+  __shared__ float wsp[4][2][SA_MAX_SPLITS];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int pair = blockIdx.x * (blockDim.x >> 5) + warp;      // (query, head)
   if (pair >= pairs) return;
-  const int lane = threadIdx.x & 31;
   const int m = pair / H, h = pair - m * H;
-  float ov[8];                                   // vdim <= 256: up to eight values per lane
-#pragma unroll
-  for (int e = 0; e < 8; ++e) ov[e] = 0.f;
   for (int mp = 0; mp < maps; ++mp) {
     const size_t sp = (size_t)pair * maps + mp;  // the (query, head, map) the attention kernel numbered
-    const float* snk = sink ? sink + (size_t)h * maps + mp : nullptr;
-    float mx = snk ? *snk : -INFINITY;
-    for (int s = 0; s < splits; ++s) mx = fmaxf(mx, part_ml[(sp * splits + s) * 2]);
-    float den = snk ? expf(*snk - mx) : 0.f;
-    for (int s = 0; s < splits; ++s) {
-      const float ms = part_ml[(sp * splits + s) * 2];
-      if (ms != -INFINITY) den += part_ml[(sp * splits + s) * 2 + 1] * expf(ms - mx);
-    }
-    const float inv = 1.f / den;
-    const float wgt = mp == 0 ? 1.f : -lambda;
+    const float snk = sink ? sink[(size_t)h * maps + mp] : -INFINITY;
+    float ms[SA_MAX_SPLITS / 32], ls[SA_MAX_SPLITS / 32];
+    float mx = snk;
 #pragma unroll
-    for (int e = 0; e < 8; ++e) {
-      const int c = lane + e * 32;
-      if (c >= vdim) continue;
-      float o = 0.f;
-      for (int s = 0; s < splits; ++s) {
-        const float ms = part_ml[(sp * splits + s) * 2];
-        if (ms != -INFINITY) o += part_acc[(sp * splits + s) * vdim + c] * expf(ms - mx);
-      }
-      ov[e] += wgt * (o * inv);
+    for (int e = 0; e < SA_MAX_SPLITS / 32; ++e) {
+      const int sidx = lane + e * 32;
+      ms[e] = sidx < splits ? part_ml[(sp * splits + sidx) * 2] : -INFINITY;
+      ls[e] = sidx < splits ? part_ml[(sp * splits + sidx) * 2 + 1] : 0.f;
+      mx = fmaxf(mx, ms[e]);
     }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    float den = 0.f;
+#pragma unroll
+    for (int e = 0; e < SA_MAX_SPLITS / 32; ++e) {
+      ms[e] = ms[e] == -INFINITY ? 0.f : expf(ms[e] - mx);
+      den += ls[e] * ms[e];
+    }
+    den = warp_sum(den);
+    if (sink) den += expf(snk - mx);
+    const float wgt = (mp == 0 ? 1.f : -lambda) / den;
+#pragma unroll
+    for (int e = 0; e < SA_MAX_SPLITS / 32; ++e)
+      if (lane + e * 32 < splits) wsp[warp][mp][lane + e * 32] = ms[e] * wgt;
+  }
+  __syncwarp();
+  float ov[8];                                   // vdim <= 256: up to eight values per lane
+#pragma unroll
+  for (int e = 0; e < 8; ++e) {
+    const int c = lane + e * 32;
+    float o = 0.f;
+    if (c < vdim)
+      for (int mp = 0; mp < maps; ++mp) {
+        const float* acc = part_acc + ((size_t)pair * maps + mp) * splits * vdim + c;
+        for (int s2 = 0; s2 < splits; ++s2) o = fmaf(acc[(size_t)s2 * vdim], wsp[warp][mp][s2], o);
+      }
+    ov[e] = o;
   }
   float k = 1.f;
   if (maps > 1) {
@@ -310,7 +327,7 @@ __global__ void softmax_attn_merge_kernel(const float* __restrict__ part_ml, con
 #pragma unroll
   for (int e = 0; e < 8; ++e) {
     const int c = lane + e * 32;
-    if (c >= vdim) break;
+    if (c >= vdim) continue;
     float o = ov[e] * k;
     if (gate) o *= 1.f / (1.f + expf(-dt<T>::ld(gate, (size_t)m * gate_stride + (size_t)h * vdim + c)));
     dt<T>::st(y, (size_t)m * H * vdim + (size_t)h * vdim + c, o);
@@ -676,7 +693,7 @@ int ll_softmax_attn_maps(const void* q, int q_stride, const void* gate, int gate
                          float eps, float* scratch, void* y, ll_stream stream) {
   LL_CHECK_ARG(q && kc && vc && pos_ids && y, "softmax_attn: null pointer");
   LL_CHECK_ARG(B >= 0 && T >= 0 && H > 0 && G > 0 && H % G == 0 && dim > 0 && vdim > 0 && ring > 0 && window >= 0 && chunk >= 0 &&
-                   splits >= 1 && (maps == 1 || maps == 2),
+                   splits >= 1 && splits <= SA_MAX_SPLITS && (maps == 1 || maps == 2),
                "bad softmax_attn arguments");
   if (dim > 256 || vdim > 256) {
     set_error("softmax_attn: heads of %d / %d dimensions (up to 256)", dim, vdim);

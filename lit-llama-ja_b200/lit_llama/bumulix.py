@@ -330,8 +330,9 @@ class Bumulix(PortionedDecoder):
             spec = blk.mix.spec
             if layer.kind == "attention":
                 span = min(spec.reach if spec.reach is not None else (1 << 30), ring)
-                # few queries: share a long look-back among blocks
-                splits = max(1, min(64, (2 * sms) // max(1, (M * spec.heads * spec.maps + 3) // 4), (span + 127) // 128))
+                # few queries: share the look-back among blocks, down to 32 keys each (a group of lanes walks its keys one
+                # after the other, every step a round trip to memory)
+                splits = max(1, min(64, (2 * sms) // max(1, (M * spec.heads * spec.maps + 3) // 4), (span + 31) // 32))
                 y = blk.mix(h, B, T, pos_ids, self.kv_caches[at:at + 2], None, splits)
             else:
                 splits = max(1, min(16, (2 * sms) // max(1, M * ((spec.heads + 31) // 32)), (ring + 63) // 64))
