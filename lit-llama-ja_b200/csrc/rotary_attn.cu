@@ -375,7 +375,7 @@ static int sa_dispatch(const void* q, int q_stride, const void* gate, int gate_s
 // Prompts in bf16 (mma.sync m16n8k16, fp32 accumulation).  A block of four warps owns 64 consecutive queries of one head,
 // 16 per warp, whose fragments stay in registers; the keys the tile can see are walked 64 at a time through shared memory
 // (cp.async into two stages, the next tile under the current one's math; rows found by position % ring, dimensions beyond
-// the head's size zero-filled up to D).  S = Q K^T, then scale,
+// the rows' sizes zero-filled up to DK / DV).  S = Q K^T, then scale,
 // cap and mask on the accumulator fragments, an online softmax per row in fp32, and O += P V with the weights split into
 // two bf16 terms p = hi + lo (two products), so that what meets the values carries 16 bits of the fp32 weight and not 8.
 // The sink joins the denominator and the gate multiplies the output in the epilogue.
@@ -408,13 +408,14 @@ __device__ __forceinline__ float tm_tanh(float x) { return 1.f - __fdividef(2.f,
 
 // MAPS = 2: the block walks its keys once per map (queries and keys of the map, the same values) and keeps the first map's
 // normalised output in registers until the second is there; the difference, its unit norm and `post` are the epilogue.
-template <int D, int MAPS>
+// DK / DV: the padded sizes of a key row and of a value row (a map's keys may be half as wide as the values).
+template <int DK, int DV, int MAPS>
 __global__ void __launch_bounds__(TM_THREADS, MAPS == 1 ? 3 : 2) softmax_attn_mma_kernel(
     const __nv_bfloat16* __restrict__ q, int q_stride, const __nv_bfloat16* __restrict__ gate, int gate_stride,
     const __nv_bfloat16* __restrict__ kc, const __nv_bfloat16* __restrict__ vc, const int32_t* __restrict__ pos_ids,
     const float* __restrict__ sink, float scale, float softcap, int Tn, int H, int G, int dim, int vdim, int window, int chunk, int ring,
     float lambda, float post, float eps, __nv_bfloat16* __restrict__ y) {
-  constexpr int LD = D + 8, CH = D / 8, STAGE = 2 * TM_K * LD;      // a stage: 64 key rows, then 64 value rows
+  constexpr int LD = DK + 8, CH = DK / 8, LV = DV + 8, CV = DV / 8, STAGE = TM_K * (LD + LV);      // a stage: 64 key rows, then 64 value rows
   extern __shared__ __align__(16) unsigned char tm_smem[];
   __nv_bfloat16* const stages = (__nv_bfloat16*)tm_smem;
   __nv_bfloat16* Ks = stages;                                       // (the queries pass through stage 0 first)
@@ -432,7 +433,7 @@ __global__ void __launch_bounds__(TM_THREADS, MAPS == 1 ? 3 : 2) softmax_attn_mm
   const int wlo_last = sa_first_visible(whi, window, chunk);
   const int kt0 = sa_first_visible(p0, window, chunk);
   const __nv_bfloat16* vbase = vc + ((size_t)b * ring * G + g) * vdim;
-  float first[MAPS == 1 ? 1 : D / 8][4];         // the first map's output, rows and columns as in o
+  float first[MAPS == 1 ? 1 : DV / 8][4];         // the first map's output, rows and columns as in o
 #pragma unroll 1
   for (int mp = 0; mp < MAPS; ++mp) {
   const int hq = h * MAPS + mp, GK = G * MAPS;
@@ -444,13 +445,13 @@ __global__ void __launch_bounds__(TM_THREADS, MAPS == 1 ? 3 : 2) softmax_attn_mm
     *(uint4*)&Ks[r * LD + ch * 8] = val;
   }
   __syncthreads();
-  uint32_t qf[D / 16][4];
+  uint32_t qf[DK / 16][4];
 #pragma unroll
-  for (int kk = 0; kk < D / 16; ++kk) tm_ldmatrix_x4(qf[kk], &Ks[(warp * 16 + (lane & 15)) * LD + kk * 16 + (lane >> 4) * 8]);
+  for (int kk = 0; kk < DK / 16; ++kk) tm_ldmatrix_x4(qf[kk], &Ks[(warp * 16 + (lane & 15)) * LD + kk * 16 + (lane >> 4) * 8]);
   __syncthreads();
-  float o[D / 8][4];
+  float o[DV / 8][4];
 #pragma unroll
-  for (int n = 0; n < D / 8; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
+  for (int n = 0; n < DV / 8; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
   float mrow[2] = {-INFINITY, -INFINITY}, lrow[2] = {0.f, 0.f};
   const __nv_bfloat16* kbase = kc + ((size_t)b * ring * GK + (g * MAPS + mp)) * dim;
   // the next tile's rows are copied under the current tile's math: two stages, one cp.async group per tile
@@ -463,8 +464,13 @@ __global__ void __launch_bounds__(TM_THREADS, MAPS == 1 ? 3 : 2) softmax_attn_mm
       const size_t slot = (size_t)(j % ring);
       if (j <= khi && ch * 8 < dim) tm_cp_async16(&Kd[r * LD + ch * 8], kbase + slot * GK * dim + ch * 8);
       else *(uint4*)&Kd[r * LD + ch * 8] = zero4;
-      if (j <= khi && ch * 8 < vdim) tm_cp_async16(&Vd[r * LD + ch * 8], vbase + slot * G * vdim + ch * 8);
-      else *(uint4*)&Vd[r * LD + ch * 8] = zero4;
+    }
+    for (int c = tid; c < TM_K * CV; c += TM_THREADS) {
+      const int r = c / CV, ch = c - r * CV;
+      const int j = kt + r;
+      const size_t slot = (size_t)(j % ring);
+      if (j <= khi && ch * 8 < vdim) tm_cp_async16(&Vd[r * LV + ch * 8], vbase + slot * G * vdim + ch * 8);
+      else *(uint4*)&Vd[r * LV + ch * 8] = zero4;
     }
     asm volatile("cp.async.commit_group;" ::: "memory");
   };
@@ -487,7 +493,7 @@ __global__ void __launch_bounds__(TM_THREADS, MAPS == 1 ? 3 : 2) softmax_attn_mm
 #pragma unroll
       for (int n = 0; n < TM_K / 8; ++n) sc[n][0] = sc[n][1] = sc[n][2] = sc[n][3] = 0.f;
 #pragma unroll
-      for (int kk = 0; kk < D / 16; ++kk) {
+      for (int kk = 0; kk < DK / 16; ++kk) {
 #pragma unroll
         for (int np = 0; np < TM_K / 16; ++np) {
           uint32_t bf[4];
@@ -521,7 +527,7 @@ __global__ void __launch_bounds__(TM_THREADS, MAPS == 1 ? 3 : 2) softmax_attn_mm
         lrow[rr] *= corr[rr];
       }
 #pragma unroll
-      for (int n = 0; n < D / 8; ++n) o[n][0] *= corr[0], o[n][1] *= corr[0], o[n][2] *= corr[1], o[n][3] *= corr[1];
+      for (int n = 0; n < DV / 8; ++n) o[n][0] *= corr[0], o[n][1] *= corr[0], o[n][2] *= corr[1], o[n][3] *= corr[1];
 #pragma unroll
       for (int n = 0; n < TM_K / 8; ++n)
 #pragma unroll
@@ -538,9 +544,9 @@ __global__ void __launch_bounds__(TM_THREADS, MAPS == 1 ? 3 : 2) softmax_attn_mm
         tm_split2(sc[2 * ks + 1][0], sc[2 * ks + 1][1], ah[2], al[2]);
         tm_split2(sc[2 * ks + 1][2], sc[2 * ks + 1][3], ah[3], al[3]);
 #pragma unroll
-        for (int dp = 0; dp < D / 16; ++dp) {
+        for (int dp = 0; dp < DV / 16; ++dp) {
           uint32_t bf[4];
-          tm_ldmatrix_x4_trans(bf, &Vs[(ks * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * LD + dp * 16 + (lane >> 4) * 8]);
+          tm_ldmatrix_x4_trans(bf, &Vs[(ks * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * LV + dp * 16 + (lane >> 4) * 8]);
           mma_bf16_16816(o[2 * dp], ah[0], ah[1], ah[2], ah[3], bf[0], bf[1]);
           mma_bf16_16816(o[2 * dp + 1], ah[0], ah[1], ah[2], ah[3], bf[2], bf[3]);
           mma_bf16_16816(o[2 * dp], al[0], al[1], al[2], al[3], bf[0], bf[1]);
@@ -567,14 +573,14 @@ __global__ void __launch_bounds__(TM_THREADS, MAPS == 1 ? 3 : 2) softmax_attn_mm
   if (MAPS == 2) {
     if (mp == 0) {
 #pragma unroll
-      for (int n = 0; n < D / 8; ++n)
+      for (int n = 0; n < DV / 8; ++n)
 #pragma unroll
         for (int e = 0; e < 4; ++e) first[MAPS == 1 ? 0 : n][e] = o[n][e] * fin[e >> 1];
       continue;                                  // (the loop's last barrier has passed: stage 0 is free for the next queries)
     }
     float ss[2] = {0.f, 0.f};
 #pragma unroll
-    for (int n = 0; n < D / 8; ++n)
+    for (int n = 0; n < DV / 8; ++n)
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
         const float d = first[MAPS == 1 ? 0 : n][e] - lambda * (o[n][e] * fin[e >> 1]);
@@ -595,7 +601,7 @@ __global__ void __launch_bounds__(TM_THREADS, MAPS == 1 ? 3 : 2) softmax_attn_mm
     const float f = fin[rr];
     const size_t m = (size_t)b * Tn + t0 + r;
 #pragma unroll
-    for (int n = 0; n < D / 8; ++n) {
+    for (int n = 0; n < DV / 8; ++n) {
       const int c = n * 8 + (lane & 3) * 2;
       if (c < vdim) {                            // vdim is a multiple of 8: the pair is inside together
         float v0 = o[n][rr * 2] * f, v1 = o[n][rr * 2 + 1] * f;
@@ -611,18 +617,18 @@ __global__ void __launch_bounds__(TM_THREADS, MAPS == 1 ? 3 : 2) softmax_attn_mm
   }  // maps
 }
 
-template <int D, int MAPS>
+template <int DK, int DV, int MAPS>
 static int tm_launch(const void* q, int q_stride, const void* gate, int gate_stride, const void* kc, const void* vc, const int32_t* pos_ids,
                      const float* sink, float scale, float softcap, int B, int Tn, int H, int G, int dim, int vdim, int window, int chunk,
                      int ring, const DiffMaps& dm, void* y, cudaStream_t st) {
   const dim3 grid((Tn + TM_Q - 1) / TM_Q, H, B);
-  constexpr int smem = 2 * 2 * TM_K * (D + 8) * (int)sizeof(__nv_bfloat16);
+  constexpr int smem = 2 * TM_K * (DK + 8 + DV + 8) * (int)sizeof(__nv_bfloat16);
   static bool sized = false;
   if (!sized) {
-    LL_CUDA(cudaFuncSetAttribute(softmax_attn_mma_kernel<D, MAPS>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    LL_CUDA(cudaFuncSetAttribute(softmax_attn_mma_kernel<DK, DV, MAPS>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     sized = true;
   }
-  softmax_attn_mma_kernel<D, MAPS><<<grid, TM_THREADS, smem, st>>>(
+  softmax_attn_mma_kernel<DK, DV, MAPS><<<grid, TM_THREADS, smem, st>>>(
       (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)gate, gate_stride, (const __nv_bfloat16*)kc, (const __nv_bfloat16*)vc,
       pos_ids, sink, scale, softcap, Tn, H, G, dim, vdim, window, chunk, ring, dm.lambda, dm.post, dm.eps, (__nv_bfloat16*)y);
   LL_LAUNCH_OK("softmax_attn_mma_kernel");
@@ -704,16 +710,22 @@ int ll_softmax_attn_maps(const void* q, int q_stride, const void* gate, int gate
   const DiffMaps dm{maps, diff_lambda, diff_post, eps};
   if (form == 0 && tm_supported(dtype, T, dim, vdim, q_stride, gate ? gate_stride : 0, splits)) {
     const int d = dim > vdim ? dim : vdim;
+    if (maps == 1) {           // one map: key and value rows padded alike
 #define LL_TM(DD)                                                                                                                   \
-  if (d <= DD) {                                                                                                                    \
-    if (maps == 1)                                                                                                                  \
-      return tm_launch<DD, 1>(q, q_stride, gate, gate_stride, kc, vc, pos_ids, sink, scale, softcap, B, T, H, G, dim, vdim, window,  \
-                              chunk, ring, dm, y, st);                                                                              \
-    return tm_launch<DD, 2>(q, q_stride, gate, gate_stride, kc, vc, pos_ids, sink, scale, softcap, B, T, H, G, dim, vdim, window,    \
-                            chunk, ring, dm, y, st);                                                                                \
-  }
-    LL_TM(32) LL_TM(64) LL_TM(96) LL_TM(128)
+  if (d <= DD)                                                                                                                      \
+    return tm_launch<DD, DD, 1>(q, q_stride, gate, gate_stride, kc, vc, pos_ids, sink, scale, softcap, B, T, H, G, dim, vdim, window, \
+                                chunk, ring, dm, y, st);
+      LL_TM(32) LL_TM(64) LL_TM(96) LL_TM(128)
 #undef LL_TM
+    }
+#define LL_TM2(KK, VV)                                                                                                              \
+  if (dim <= KK && vdim <= VV)                                                                                                      \
+    return tm_launch<KK, VV, 2>(q, q_stride, gate, gate_stride, kc, vc, pos_ids, sink, scale, softcap, B, T, H, G, dim, vdim, window, \
+                                chunk, ring, dm, y, st);
+#define LL_TM2_ROW(KK) LL_TM2(KK, 32) LL_TM2(KK, 64) LL_TM2(KK, 96) LL_TM2(KK, 128)
+    LL_TM2_ROW(32) LL_TM2_ROW(64) LL_TM2_ROW(96) LL_TM2_ROW(128)
+#undef LL_TM2_ROW
+#undef LL_TM2
   }
   LL_CHECK_ARG(scratch || (splits == 1 && maps == 1), "softmax_attn: split key ranges and several maps meet in scratch memory");
   if (dtype == LL_F32)

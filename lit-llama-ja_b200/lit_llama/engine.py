@@ -25,6 +25,7 @@ import torch.distributed as dist
 
 from . import _native as N
 from .quantization import ColBlockQuantizedLinear
+from .stepping import graph_capture
 
 
 def _unwrap(lin):
@@ -337,7 +338,7 @@ class DecodeEngine:
         torch.cuda.current_stream().wait_stream(s)
         torch.cuda.synchronize()
         g = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(g):
+        with graph_capture(g):
             self._run_step()
         self.graph = g
 
@@ -407,7 +408,7 @@ class DecodeEngine:
         self.draw.zero_()
         torch.cuda.synchronize()
         g = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(g):
+        with graph_capture(g):
             self._run_sampled(temperature, top_k)
         self.sample_graphs[key] = g
 

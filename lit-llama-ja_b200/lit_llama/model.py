@@ -22,6 +22,7 @@ import torch.nn as nn
 from torch.nn import functional as F
 
 from . import _native as N
+from .stepping import graph_capture
 from .utils import find_multiple
 
 KVCache = Tuple[torch.Tensor, torch.Tensor]
@@ -318,7 +319,7 @@ class LLaMA(nn.Module):
             torch.cuda.current_stream().wait_stream(side)
             torch.cuda.synchronize()
             g = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(g):
+            with graph_capture(g):
                 out = self._forward_modules(s_idx, max_seq_length, s_pos)
             ent = self._step_graphs[key] = dict(graph=g, idx=s_idx, pos=s_pos, out=out, kv=list(self.kv_caches),
                                                 kv0=self.kv_caches[0][0].data_ptr())

@@ -8,6 +8,8 @@ token and its position in device tensors the graph reads.  A model supplies the 
 """
 from __future__ import annotations
 
+import contextlib
+import gc
 import os
 from typing import Dict, Optional
 
@@ -15,6 +17,23 @@ import torch
 import torch.nn as nn
 
 from . import _native as N
+
+
+@contextlib.contextmanager
+def graph_capture(g: "torch.cuda.CUDAGraph"):
+    """``with torch.cuda.graph(g)`` that no garbage collection can break.  A model that was dropped while it still held
+    captured steps is a dead reference cycle; when the collector finds it, the graphs inside are destroyed, and destroying a
+    graph while ANY stream of the process captures invalidates that capture (its next launch then fails).  So the dead
+    cycles are collected before the capture begins and the collector rests until it has ended."""
+    gc.collect()
+    was_enabled = gc.isenabled()
+    gc.disable()
+    try:
+        with torch.cuda.graph(g):
+            yield
+    finally:
+        if was_enabled:
+            gc.enable()
 
 
 class PortionedDecoder(nn.Module):
@@ -109,7 +128,7 @@ class PortionedDecoder(nn.Module):
             torch.cuda.current_stream().wait_stream(side)
             torch.cuda.synchronize()
             g = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(g):
+            with graph_capture(g):
                 out = self._forward_portion(s_idx, s_pos, None)
             ent = self._step_graphs[key] = dict(graph=g, idx=s_idx, pos=s_pos, out=out)
         ent["idx"].copy_(idx)
