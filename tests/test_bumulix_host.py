@@ -26,14 +26,14 @@ def test_config_from_file_and_shapes():
     c = BumulixConfig.from_dict(cfg, shapes_of(W))
     assert (c.vocab, c.width, c.streams, c.copies, c.logit_softcap, c.residual_mult) == (61, 40, 3, 3, 9.0, 0.7)
     assert [l.kind for l in c.layers] == ["latent_attention", "attention", "attention", "attention", "latent_attention",
-                                          "latent_attention", "attention"]
-    assert [l.weights_of for l in c.layers] == [None, None, 1, None, 0, None, 3]
+                                          "attention", "latent_attention"]
+    assert [l.weights_of for l in c.layers] == [None, None, 1, 5, 0, None, None]
     a = c.layers[1].mixer
     assert (a.heads, a.kv_heads, a.dim, a.vdim, a.window, a.maps, a.diff, a.gate, a.reach) == (6, 2, 8, 12, 5, 2, 0.3, False, 5)
     l = c.layers[0].mixer
     assert (l.heads, l.nope_dim, l.rot_dim, l.v_dim, l.kv_rank, l.q_rank, l.gate, l.rot_layout, l.window) == \
         (3, 6, 4, 10, 12, 7, "element", "half", None)
-    assert l.rotary.scaling == "yarn" and c.layers[5].mixer.rotary.scaling is None
+    assert l.rotary.scaling == "yarn" and c.layers[6].mixer.rotary.scaling is None
     assert c.layers[1].ff is None and c.layers[3].ff == 20
     # sizes the file leaves out come from the tensors
     gone = ("heads", "kv_heads", "kv_rank", "q_rank")

@@ -73,7 +73,7 @@ def test_ring_wraps_and_slots_are_reused(mixed, portion):
     cfg, W, folder, toks, want = mixed
     m = load(folder, torch.float32, prefill_portion=portion)
     got = run_schedule(m, toks, [30] + [1] * 15, 64)[0]
-    assert m._rings == (64, 5 - 1 + portion, 5 - 1 + portion, 9 - 1 + portion, 64, 64, 9 - 1 + portion)
+    assert m._rings == (64, 5 - 1 + portion, 5 - 1 + portion, 9 - 1 + portion, 64, 9 - 1 + portion, 64)
     assert len({t.data_ptr() for t in m.kv_caches}) == 4 * 2 + 3
     assert rel_err(got, want) < TOL32
     got = run_schedule(m, toks, [7, 2, 21, 15], 64)[0]

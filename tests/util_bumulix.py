@@ -44,12 +44,10 @@ def dense(ff):
 
 def model_cfg(vocab, width, layers, streams=2, eps=1e-5, mult=0.6, cap=12.0):
     """``layers``: (mixer entry, feed-forward entry or None) or an int j: the layer computes with layer j's tensors."""
-    out = []
-    for l in layers:
-        if isinstance(l, int):
-            out.append(dict(out[l], weights_of=l))
-        else:
-            out.append(dict(l[0], mlp=l[1]))
+    out = [None if isinstance(l, int) else dict(l[0], mlp=l[1]) for l in layers]
+    for i, l in enumerate(layers):
+        if isinstance(l, int):                 # earlier or later in the list
+            out[i] = dict(out[l], weights_of=l)
     cfg = {"architecture": "Bumulix", "vocab": vocab, "width": width, "norm": {"eps": eps}, "residual_mult": mult, "layers": out}
     if streams is not None:
         cfg["streams"] = streams
@@ -102,15 +100,15 @@ def random_weights(cfg, seed=0, qk_gain=2.0, layer_scale=True):
 def case_mixed(seed=0):
     """Sizes that share nothing with each other; both mixers in an order of its own, three copies of the stream, grouped
     key/value heads, two windows, layers with and without feed-forward, layers that compute with another layer's tensors
-    (one of them before a layer with tensors of its own)."""
+    (one of them names a LATER layer)."""
     layers = [
         (latent(3, 6, 4, 10, 12, 7, base=50.0, yarn=(4.0, 32, 8.0, 1.0)), dense(24)),
         (diff_attn(6, 2, 8, 12, window=5, diff=0.3, scale=0.5), None),
         1,
-        (diff_attn(2, 1, 16, 8, window=9, diff=0.6), dense(20)),
+        5,
         0,
+        (diff_attn(2, 1, 16, 8, window=9, diff=0.6), dense(20)),
         (latent(2, 8, 8, 4, 5, 9, base=20.0, yarn=None), None),
-        3,
     ]
     cfg = model_cfg(61, 40, layers, streams=3, eps=1e-4, mult=0.7, cap=9.0)
     return cfg, random_weights(cfg, seed, qk_gain=1.2)
