@@ -156,7 +156,7 @@ class BumulixConfig:
 
 
 class HyperConnection(nn.Module):
-    """The stream coefficients of one sublayer: ``w_in [S]`` (read), ``mix [S, S]`` indexed [from, to] and ``w_out [S]``
+    """The stream coefficients of one sublayer: ``w_in [S]`` (read), ``mix [S, S]`` (row: the copy read, column: the copy written) and ``w_out [S]``
     (write), fp32.  A model with one plain stream has ``mix`` = None and ``w_out`` = [1]."""
 
     def __init__(self, streams: Optional[int], device) -> None:

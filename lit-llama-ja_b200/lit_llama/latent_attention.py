@@ -14,8 +14,8 @@ queries and window.
 Variations, all parameters of the spec:
 * ``q_rank``: the queries pass a latent of their own, ``q = W_uq (rmsnorm(W_dq h) * w_q)``; the input projection is then
   ``[dq | g | d]``.
-* ``gate``: "head" (one logit per head, as above), "element" (``sigmoid(W_g h)`` of heads * v_dim numbers multiplies the
-  concatenated heads element by element, after W_uv) or "none".
+* ``gate``: "head" (one logit per head, as above), "element" (``sigmoid(W_g h)`` holds heads * v_dim numbers, one for every
+  number the heads put out; applied after W_uv) or "none".
 * ``rot_layout``: "interleaved" pairs dimension 2i with 2i+1; "half" pairs i with i + rot_dims/2.  The kernels turn
   interleaved pairs; a "half" checkpoint has the rows of its rotated query and key parts reordered once at load time (the
   same reordering on both sides of the dot product leaves the scores as they are).

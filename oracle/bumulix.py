@@ -95,8 +95,8 @@ def rotate_half(x, rot, positions):
 
 # ------------------------------------------------------------------------------------------------ mixers
 def differential_attention(h, W, m, eps):
-    """h [T, E] -> [T, E].  Per head two score maps (q and k rows laid out head by head as [map 1 | map 2]) over the same
-    values; o = a1 - lam * a2, divided by its root mean square over the head's values, times (1 - diff)."""
+    """h [T, E] -> [T, E].  Every head scores its keys twice: a head's q rows (a key/value head's k rows) hold map 0, then map 1, and
+    both maps weigh the same values; o = a1 - lam * a2, divided by its root mean square over the head's values, times (1 - diff)."""
     T = h.shape[0]
     H, G, d, dv = int(m["heads"]), int(m["kv_heads"]), int(m["dim"]), int(m["vdim"])
     diff = float(m["diff"])
